@@ -1,0 +1,412 @@
+// Block-level-partitioned CSR SpMM for sm_100a:  Y[n_rows x dim] = A * X,
+// A given as the degree-ordered (idx, val) arrays plus `.block4` metadata
+// (one tuple {degree, row_begin, loc_begin, info} per block of <= 384
+// nonzeros; decode rules of spmm_accel.cu:18-34).
+//
+// Work decomposition.  A thread block ("unit") takes SPMM_WARPS consecutive
+// tuples, one per warp.  A warp first stages its tuple's (col, val) slice --
+// at most 384 pairs -- into shared memory with coalesced loads, then walks it.
+// The columns of one dense row are covered by a "slot" of S lanes, each lane
+// holding a float4 (the counterpart of the reference's combined warp,
+// spmm_accel.cu:36-53, with 16-byte instead of 4-byte lanes); a warp therefore
+// works on 32/S nonzeros at a time.  Rows of degree <= 32 are given one slot
+// each, longer rows are split over the slots of the warp and folded with
+// butterfly shuffles.  Accumulators live in registers.
+//
+// Heavy rows (degree > 384) span several tuples.  Their per-tuple partial sums
+// meet in shared memory and are added in tuple order; a row that is contained
+// in one unit is then stored directly.  A row that crosses a unit boundary
+// leaves one partial per unit in a small "carry" array (at most two per unit),
+// and spmm_carry_kernel adds those in unit order.  Every element of Y is thus
+// written exactly once with a plain store, in a fixed order of additions: no
+// atomics, no dependence on what Y held before, bit-identical from run to run.
+// Rows no tuple covers (degree 0) are zero-filled by extra blocks of the same
+// launch.
+#pragma once
+#include "primitives.cuh"
+#include "ptx.cuh"
+
+namespace agcn {
+
+constexpr int SPMM_DEG_BOUND = 384;    // format constant of .block4 (spmm_accel.cu:11)
+constexpr int SPMM_WARPS = 8;          // tuples per unit, one per warp
+constexpr int SPMM_THREADS = SPMM_WARPS * 32;
+constexpr int SPMM_PANEL = 128;        // dense columns covered by one launch
+constexpr int SPMM_ZERO_ROWS_PER_BLOCK = 64;
+
+struct SpmmParams {
+    const int4 *block4;
+    int64_t n_blocks;
+    int64_t n_units;
+    const int *idx;
+    const float *val;
+    const float *x;     // first column of the panel
+    int64_t ldx;        // floats between consecutive rows of X
+    float *y;
+    int64_t ldy;
+    int dim;            // columns in this panel, 1..SPMM_PANEL
+    const int2 *unit_carry;   // per unit: carry slot of a row entering / leaving the unit, or -1
+    float *carry;             // [n_carry][SPMM_PANEL]
+    const int *zero_rows;     // rows no tuple covers
+    int64_t n_zero_rows;
+};
+
+struct TupleView {
+    int row0, loc, n_rows, row_nz;
+    bool valid, small;
+};
+
+__device__ __forceinline__ TupleView decode_tuple(const int4 *__restrict__ block4, int64_t e, int64_t n_blocks)
+{
+    TupleView t;
+    t.valid = e < n_blocks;
+    const int4 b = t.valid ? __ldg(block4 + e) : make_int4(0, 0, 0, 0);
+    t.small = b.x <= SPMM_DEG_BOUND;
+    t.row0 = b.y;
+    t.loc = b.z;
+    t.n_rows = t.small ? (b.w & 0xffff) : 1;
+    t.row_nz = t.small ? b.x : b.w;
+    if (!t.valid) { t.n_rows = 0; t.row_nz = 0; }
+    return t;
+}
+
+// ---------------------------------------------------------------------------
+// gather-accumulate over the staged pairs  first, first+step, ... < count
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void fma4(float4 &acc, float a, const float4 &v)
+{
+    acc.x = fmaf(a, v.x, acc.x);
+    acc.y = fmaf(a, v.y, acc.y);
+    acc.z = fmaf(a, v.z, acc.z);
+    acc.w = fmaf(a, v.w, acc.w);
+}
+
+__device__ __forceinline__ float4 gather_vec4(const int2 *pairs, int count, int first, int step,
+                                              const float *__restrict__ x, int64_t ldx, bool active)
+{
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (!active) return acc;
+    int i = first;
+    for (; i + 3 * step < count; i += 4 * step) {
+        const int2 p0 = pairs[i], p1 = pairs[i + step], p2 = pairs[i + 2 * step], p3 = pairs[i + 3 * step];
+        const float4 v0 = ld_x4(x + (int64_t)p0.x * ldx);
+        const float4 v1 = ld_x4(x + (int64_t)p1.x * ldx);
+        const float4 v2 = ld_x4(x + (int64_t)p2.x * ldx);
+        const float4 v3 = ld_x4(x + (int64_t)p3.x * ldx);
+        fma4(acc, __int_as_float(p0.y), v0);
+        fma4(acc, __int_as_float(p1.y), v1);
+        fma4(acc, __int_as_float(p2.y), v2);
+        fma4(acc, __int_as_float(p3.y), v3);
+    }
+    for (; i < count; i += step) {
+        const int2 p0 = pairs[i];
+        fma4(acc, __int_as_float(p0.y), ld_x4(x + (int64_t)p0.x * ldx));
+    }
+    return acc;
+}
+
+constexpr int SPMM_SCALAR_COLS = SPMM_PANEL / 32;   // columns per lane in scalar mode
+
+__device__ __forceinline__ void gather_scalar(const int2 *pairs, int count, const float *__restrict__ x,
+                                              int64_t ldx, int dim, float (&acc)[SPMM_SCALAR_COLS])
+{
+    const int lane = lane_id();
+#pragma unroll
+    for (int k = 0; k < SPMM_SCALAR_COLS; k++) acc[k] = 0.f;
+    for (int i = 0; i < count; i++) {
+        const int2 p = pairs[i];
+        const float a = __int_as_float(p.y);
+        const float *xr = x + (int64_t)p.x * ldx;
+#pragma unroll
+        for (int k = 0; k < SPMM_SCALAR_COLS; k++) {
+            const int c = lane + 32 * k;
+            if (c < dim) acc[k] = fmaf(a, ld_x1(xr + c), acc[k]);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// main kernel.  S = lanes per slot in float4 mode (4, 8, 16 or 32; needs
+// dim % 4 == 0, dim <= 4*S and 16-byte aligned rows); S = 0 is the scalar
+// mode for every other dim (lane l owns columns l, l+32, l+64, l+96).
+// ---------------------------------------------------------------------------
+template <int S>
+__global__ void __launch_bounds__(SPMM_THREADS)
+spmm_units_kernel(const SpmmParams p)
+{
+    __shared__ int2 s_pair[SPMM_WARPS][SPMM_DEG_BOUND];
+    __shared__ __align__(16) float s_part[SPMM_WARPS][SPMM_PANEL];
+    __shared__ int s_row[SPMM_WARPS];
+    __shared__ int s_big[SPMM_WARPS];
+
+    constexpr bool VEC = S > 0;
+    constexpr int LANES = VEC ? S : 32;
+    constexpr int NS = 32 / LANES;          // nonzeros a warp works on at a time
+    const int w = warp_id(), lane = lane_id();
+    const int slot = lane / LANES, sl = lane % LANES;
+    const int col = VEC ? sl * 4 : sl;
+    const bool active = col < p.dim;
+
+    if ((int64_t)blockIdx.x >= p.n_units) {
+        // zero-fill rows that no tuple covers
+        const int64_t zb = ((int64_t)blockIdx.x - p.n_units) * SPMM_ZERO_ROWS_PER_BLOCK;
+        for (int k = w * NS + slot; k < SPMM_ZERO_ROWS_PER_BLOCK; k += SPMM_WARPS * NS) {
+            if (zb + k >= p.n_zero_rows) break;
+            float *yr = p.y + (int64_t)p.zero_rows[zb + k] * p.ldy;
+            if (VEC) {
+                if (active) st_y4(yr + col, make_float4(0.f, 0.f, 0.f, 0.f));
+            } else {
+                for (int c = lane; c < p.dim; c += 32) yr[c] = 0.f;
+            }
+        }
+        return;
+    }
+
+    const int64_t e = (int64_t)blockIdx.x * SPMM_WARPS + w;
+    const TupleView t = decode_tuple(p.block4, e, p.n_blocks);
+    const int total = t.n_rows * t.row_nz;
+
+    // stage the tuple's (col, val) slice
+    {
+        const int *__restrict__ gi = p.idx + t.loc;
+        const float *__restrict__ gv = p.val + t.loc;
+#pragma unroll 4
+        for (int k = lane; k < total; k += 32) s_pair[w][k] = make_int2(ld_a(gi + k), __float_as_int(ld_a(gv + k)));
+    }
+    __syncwarp();
+
+    const bool big = t.valid && !t.small;
+    const int2 *pairs = s_pair[w];
+
+    if (VEC) {
+        const float *xc = p.x + col;
+        if (t.small && NS > 1 && t.row_nz <= 32) {
+            // one slot per row
+            for (int r = slot; r < t.n_rows; r += NS) {
+                const float4 acc = gather_vec4(pairs + r * t.row_nz, t.row_nz, 0, 1, xc, p.ldx, active);
+                if (active) st_y4(p.y + (int64_t)(t.row0 + r) * p.ldy + col, acc);
+            }
+        } else {
+            // the slots of the warp share each row
+            for (int r = 0; r < t.n_rows; r++) {
+                float4 acc = gather_vec4(pairs + r * t.row_nz, t.row_nz, slot, NS, xc, p.ldx, active);
+#pragma unroll
+                for (int off = LANES; off < 32; off <<= 1) {
+                    acc.x += __shfl_xor_sync(FULL_MASK, acc.x, off);
+                    acc.y += __shfl_xor_sync(FULL_MASK, acc.y, off);
+                    acc.z += __shfl_xor_sync(FULL_MASK, acc.z, off);
+                    acc.w += __shfl_xor_sync(FULL_MASK, acc.w, off);
+                }
+                if (slot == 0 && active) {
+                    if (t.small) st_y4(p.y + (int64_t)(t.row0 + r) * p.ldy + col, acc);
+                    else *reinterpret_cast<float4 *>(&s_part[w][col]) = acc;
+                }
+            }
+        }
+    } else {
+        for (int r = 0; r < t.n_rows; r++) {
+            float acc[SPMM_SCALAR_COLS];
+            gather_scalar(pairs + r * t.row_nz, t.row_nz, p.x, p.ldx, p.dim, acc);
+#pragma unroll
+            for (int k = 0; k < SPMM_SCALAR_COLS; k++) {
+                const int c = lane + 32 * k;
+                if (c < p.dim) {
+                    if (t.small) p.y[(int64_t)(t.row0 + r) * p.ldy + c] = acc[k];
+                    else s_part[w][c] = acc[k];
+                }
+            }
+        }
+    }
+
+    // heavy rows: add the per-tuple partials of a row in tuple order
+    if (lane == 0) { s_row[w] = t.row0; s_big[w] = big ? 1 : 0; }
+    __syncthreads();
+    if (!big) return;
+    if (w > 0 && s_big[w - 1] && s_row[w - 1] == t.row0) return;   // not the first tuple of its row here
+    int w_end = w + 1;
+    while (w_end < SPMM_WARPS && s_big[w_end] && s_row[w_end] == t.row0) w_end++;
+    const int64_t left = p.n_blocks - (int64_t)blockIdx.x * SPMM_WARPS;
+    const int w_last = left < SPMM_WARPS ? (int)left - 1 : SPMM_WARPS - 1;
+    const int2 uc = __ldg(p.unit_carry + blockIdx.x);
+    const bool enters = w == 0 && uc.x >= 0;            // the row began in an earlier unit
+    const bool leaves = w_end - 1 == w_last && uc.y >= 0;   // the row goes on in the next unit
+    float *dst = (enters || leaves) ? p.carry + (int64_t)(enters ? uc.x : uc.y) * SPMM_PANEL
+                                    : p.y + (int64_t)t.row0 * p.ldy;
+    if (VEC) {
+        if (slot == 0 && active) {
+            float4 sum = *reinterpret_cast<const float4 *>(&s_part[w][col]);
+            for (int ww = w + 1; ww < w_end; ww++) {
+                const float4 v = *reinterpret_cast<const float4 *>(&s_part[ww][col]);
+                sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+            }
+            st_y4(dst + col, sum);
+        }
+    } else {
+        for (int c = lane; c < p.dim; c += 32) {
+            float sum = s_part[w][c];
+            for (int ww = w + 1; ww < w_end; ww++) sum += s_part[ww][c];
+            dst[c] = sum;
+        }
+    }
+}
+
+// Adds the carried partials of every row that crosses unit boundaries, in
+// unit order, and stores the row.  One warp per carry slot; the warp of the
+// first slot of a row does the work.
+template <bool VEC>
+__global__ void __launch_bounds__(SPMM_THREADS)
+spmm_carry_kernel(const float *__restrict__ carry, const int *__restrict__ carry_row, int64_t n_carry,
+                  float *__restrict__ y, int64_t ldy, int dim)
+{
+    const int64_t s = (int64_t)blockIdx.x * SPMM_WARPS + warp_id();
+    if (s >= n_carry) return;
+    const int row = carry_row[s];
+    if (s > 0 && carry_row[s - 1] == row) return;
+    int64_t s_end = s + 1;
+    while (s_end < n_carry && carry_row[s_end] == row) s_end++;
+    const int lane = lane_id();
+    if (VEC) {
+        const int col = lane * 4;
+        if (col < dim) {
+            float4 sum = *reinterpret_cast<const float4 *>(carry + s * SPMM_PANEL + col);
+            for (int64_t q = s + 1; q < s_end; q++) {
+                const float4 v = *reinterpret_cast<const float4 *>(carry + q * SPMM_PANEL + col);
+                sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+            }
+            st_y4(y + (int64_t)row * ldy + col, sum);
+        }
+    } else {
+        for (int c = lane; c < dim; c += 32) {
+            float sum = carry[s * SPMM_PANEL + c];
+            for (int64_t q = s + 1; q < s_end; q++) sum += carry[q * SPMM_PANEL + c];
+            y[(int64_t)row * ldy + c] = sum;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// plan: built once per `.block4` array
+// ---------------------------------------------------------------------------
+constexpr int SPMM_ERR_TUPLE = 1;     // malformed tuple (degree, row count or chunk length)
+constexpr int SPMM_ERR_ROW = 2;       // rows out of range, overlapping or not ascending
+constexpr int SPMM_ERR_LOC = 4;       // nonzero range outside [0, nnz)
+constexpr int SPMM_ERR_COL = 8;       // column index outside [0, n_cols)
+
+__device__ __forceinline__ bool tuple_is_big(const int4 &b) { return b.x > SPMM_DEG_BOUND; }
+__device__ __forceinline__ int tuple_rows(const int4 &b) { return tuple_is_big(b) ? 1 : (b.w & 0xffff); }
+
+// Checks every tuple, and counts the rows that lie between tuple e-1 and
+// tuple e (gap[e]; gap[n_blocks] = rows after the last tuple).
+__global__ void __launch_bounds__(256)
+plan_check_kernel(const int4 *__restrict__ block4, int64_t n_blocks, int64_t n_rows, int64_t nnz,
+                  int *__restrict__ gap, int *__restrict__ err_flag)
+{
+    const int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e > n_blocks) return;
+    int err = 0;
+    int64_t prev_end = 0;       // first row not covered by tuples before e
+    if (e > 0) {
+        const int4 a = block4[e - 1];
+        prev_end = (int64_t)a.y + tuple_rows(a);
+    }
+    if (e == n_blocks) {
+        gap[e] = prev_end <= n_rows ? (int)(n_rows - prev_end) : 0;
+        return;
+    }
+    const int4 b = block4[e];
+    const bool big = tuple_is_big(b);
+    const int rows = tuple_rows(b);
+    const int64_t nz = big ? (int64_t)b.w : (int64_t)rows * b.x;
+    if (b.x < 1 || rows < 1 || nz < 1 || nz > SPMM_DEG_BOUND) err |= SPMM_ERR_TUPLE;
+    if (b.z < 0 || (int64_t)b.z + nz > nnz) err |= SPMM_ERR_LOC;
+    int64_t g = (int64_t)b.y - prev_end;
+    if (big && e > 0) {
+        // a later chunk of the same heavy row repeats its row id
+        const int4 a = block4[e - 1];
+        if (tuple_is_big(a) && a.y == b.y) g = 0;
+    }
+    if (b.y < 0 || (int64_t)b.y + rows > n_rows || g < 0) { err |= SPMM_ERR_ROW; g = 0; }
+    gap[e] = (int)g;
+    if (err) atomicOr(err_flag, err);
+}
+
+__global__ void __launch_bounds__(256)
+plan_check_cols_kernel(const int *__restrict__ idx, int64_t nnz, int64_t n_cols, int *__restrict__ err_flag)
+{
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    bool bad = false;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nnz; i += stride) {
+        const int c = idx[i];
+        bad |= c < 0 || c >= n_cols;
+    }
+    if (bad) atomicOr(err_flag, SPMM_ERR_COL);
+}
+
+// zero_rows[gap_offset[e] ...] = the rows of gap e
+__global__ void __launch_bounds__(256)
+plan_zero_rows_kernel(const int4 *__restrict__ block4, int64_t n_blocks, const int *__restrict__ gap,
+                      const int64_t *__restrict__ gap_offset, int *__restrict__ zero_rows)
+{
+    const int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e > n_blocks) return;
+    const int g = gap[e];
+    if (g == 0) return;
+    int64_t prev_end = 0;
+    if (e > 0) {
+        const int4 a = block4[e - 1];
+        prev_end = (int64_t)a.y + tuple_rows(a);
+    }
+    int *dst = zero_rows + gap_offset[e];
+    for (int k = 0; k < g; k++) dst[k] = (int)(prev_end + k);
+}
+
+// Does a heavy row enter unit u from the left / leave it to the right?
+__device__ __forceinline__ void unit_crossings(const int4 *__restrict__ block4, int64_t n_blocks, int64_t u,
+                                               bool &enters, bool &leaves, bool &same_row, int &row_in, int &row_out)
+{
+    const int64_t e0 = u * SPMM_WARPS;
+    const int64_t e1 = e0 + SPMM_WARPS < n_blocks ? e0 + SPMM_WARPS : n_blocks;   // one past the unit
+    const int4 first = block4[e0], last = block4[e1 - 1];
+    enters = false; leaves = false;
+    if (e0 > 0 && tuple_is_big(first)) {
+        const int4 a = block4[e0 - 1];
+        enters = tuple_is_big(a) && a.y == first.y;
+    }
+    if (e1 < n_blocks && tuple_is_big(last)) {
+        const int4 c = block4[e1];
+        leaves = tuple_is_big(c) && c.y == last.y;
+    }
+    row_in = first.y; row_out = last.y;
+    same_row = enters && leaves && first.y == last.y;
+}
+
+__global__ void __launch_bounds__(256)
+plan_count_carry_kernel(const int4 *__restrict__ block4, int64_t n_blocks, int64_t n_units, int *__restrict__ count)
+{
+    const int64_t u = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (u >= n_units) return;
+    bool en, lv, same; int ri, ro;
+    unit_crossings(block4, n_blocks, u, en, lv, same, ri, ro);
+    count[u] = (en ? 1 : 0) + (lv ? 1 : 0) - (same ? 1 : 0);
+}
+
+__global__ void __launch_bounds__(256)
+plan_assign_carry_kernel(const int4 *__restrict__ block4, int64_t n_blocks, int64_t n_units,
+                         const int64_t *__restrict__ slot_offset, int2 *__restrict__ unit_carry,
+                         int *__restrict__ carry_row)
+{
+    const int64_t u = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (u >= n_units) return;
+    bool en, lv, same; int ri, ro;
+    unit_crossings(block4, n_blocks, u, en, lv, same, ri, ro);
+    const int s = (int)slot_offset[u];
+    int2 uc = make_int2(-1, -1);
+    if (en) { uc.x = s; carry_row[s] = ri; }
+    if (lv) {
+        uc.y = same ? s : s + (en ? 1 : 0);
+        if (!same) carry_row[uc.y] = ro;
+    }
+    unit_carry[u] = uc;
+}
+
+}  // namespace agcn

@@ -1,0 +1,95 @@
+// C-ABI entry points of the block-level partitioner
+// (replaces block_level_partition.py:38-106).
+#include "host_common.h"
+#include "kernels/partition_kernels.cuh"
+
+namespace agcn {
+
+static int partition_device(const int *d_indptr, int64_t n_rows, int *d_block4, int64_t cap_blocks,
+                            int64_t *n_blocks, cudaStream_t s)
+{
+    AGCN_REQUIRE(d_indptr != nullptr && n_blocks != nullptr, "agcn_partition: null pointer");
+    AGCN_REQUIRE(n_rows > 0, "agcn_partition: empty graph (n_rows = %lld); the reference script raises IndexError here",
+                 (long long)n_rows);
+    AGCN_REQUIRE(n_rows < (int64_t)INT32_MAX, "agcn_partition: n_rows = %lld does not fit the int32 row ids of .block4",
+                 (long long)n_rows);
+    AGCN_REQUIRE(d_block4 == nullptr || aligned16(d_block4), "agcn_partition: block4 output must be 16-byte aligned");
+    *n_blocks = 0;
+
+    const int64_t tiles = ceil_div(n_rows, PART_TILE);
+    DeviceScratch scratch;
+    AGCN_ALLOC(tile_head, scratch, int, tiles);
+    AGCN_ALLOC(tile_count, scratch, int64_t, tiles);
+    AGCN_ALLOC(d_total, scratch, int64_t, 1);
+    AGCN_ALLOC(d_err, scratch, int, 1);
+    AGCN_CUDA(cudaMemsetAsync(d_err, 0, sizeof(int), s));
+
+    auto k_scan_max = single_block_scan_exclusive_kernel<int, OpMax>;
+    auto k_scan_add = single_block_scan_exclusive_kernel<int64_t, OpAdd>;
+    AGCN_KERNEL(part_run_heads_kernel, (unsigned)tiles, PART_BLOCK, s, d_indptr, n_rows, tile_head, d_err);
+    AGCN_LAUNCH_CHECK("part_run_heads_kernel");
+    AGCN_KERNEL(k_scan_max, 1, 1024, s, tile_head, tiles, -1, (int *)nullptr);
+    AGCN_LAUNCH_CHECK("single_block_scan_exclusive_kernel<max>");
+    AGCN_KERNEL(part_count_kernel, (unsigned)tiles, PART_BLOCK, s, d_indptr, n_rows, (const int *)tile_head, tile_count);
+    AGCN_LAUNCH_CHECK("part_count_kernel");
+    AGCN_KERNEL(k_scan_add, 1, 1024, s, tile_count, tiles, (int64_t)0, d_total);
+    AGCN_LAUNCH_CHECK("single_block_scan_exclusive_kernel<add>");
+
+    int64_t total = 0;
+    int err = 0;
+    AGCN_CUDA(cudaMemcpyAsync(&total, d_total, sizeof(total), cudaMemcpyDeviceToHost, s));
+    AGCN_CUDA(cudaMemcpyAsync(&err, d_err, sizeof(err), cudaMemcpyDeviceToHost, s));
+    AGCN_CUDA(cudaStreamSynchronize(s));
+    if (err != 0) {
+        set_error("agcn_partition: indptr decreases somewhere (negative degree); "
+                  "the reference script prints 'cur_degree number is wrong' and stops");
+        return AGCN_ERR_RANGE;
+    }
+    *n_blocks = total;
+    if (d_block4 == nullptr || cap_blocks == 0) return AGCN_OK;
+    if (cap_blocks < total) {
+        set_error("agcn_partition: %lld blocks needed, capacity %lld", (long long)total, (long long)cap_blocks);
+        return AGCN_ERR_CAPACITY;
+    }
+    if (total > 0) {
+        AGCN_KERNEL(part_emit_kernel, (unsigned)tiles, PART_BLOCK, s, d_indptr, n_rows, (const int *)tile_head,
+                    (const int64_t *)tile_count, reinterpret_cast<int4 *>(d_block4));
+        AGCN_LAUNCH_CHECK("part_emit_kernel");
+    }
+    AGCN_CUDA(cudaStreamSynchronize(s));
+    return AGCN_OK;
+}
+
+}  // namespace agcn
+
+extern "C" int agcn_partition_device(const int32_t *d_indptr, int64_t n_rows, int32_t *d_block4,
+                                     int64_t cap_blocks, int64_t *n_blocks, void *stream)
+{
+    agcn::clear_error();
+    return agcn::partition_device(d_indptr, n_rows, d_block4, cap_blocks, n_blocks, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int agcn_partition_host(const int32_t *h_indptr, int64_t n_rows, int32_t *h_block4,
+                                   int64_t cap_blocks, int64_t *n_blocks)
+{
+    using namespace agcn;
+    clear_error();
+    AGCN_REQUIRE(h_indptr != nullptr && n_blocks != nullptr, "agcn_partition_host: null pointer");
+    AGCN_REQUIRE(n_rows > 0, "agcn_partition_host: empty graph (n_rows = %lld); the reference script raises IndexError here",
+                 (long long)n_rows);
+    DeviceScratch scratch;
+    AGCN_ALLOC(d_indptr, scratch, int, n_rows + 1);
+    AGCN_CUDA(cudaMemcpy(d_indptr, h_indptr, (size_t)(n_rows + 1) * sizeof(int), cudaMemcpyHostToDevice));
+    int rc = partition_device(d_indptr, n_rows, nullptr, 0, n_blocks, nullptr);
+    if (rc != AGCN_OK || h_block4 == nullptr || cap_blocks == 0) return rc;
+    if (cap_blocks < *n_blocks) {
+        set_error("agcn_partition_host: %lld blocks needed, capacity %lld", (long long)*n_blocks, (long long)cap_blocks);
+        return AGCN_ERR_CAPACITY;
+    }
+    if (*n_blocks == 0) return AGCN_OK;
+    AGCN_ALLOC(d_block4, scratch, int, *n_blocks * 4);
+    rc = partition_device(d_indptr, n_rows, d_block4, *n_blocks, n_blocks, nullptr);
+    if (rc != AGCN_OK) return rc;
+    AGCN_CUDA(cudaMemcpy(h_block4, d_block4, (size_t)*n_blocks * 16, cudaMemcpyDeviceToHost));
+    return AGCN_OK;
+}

@@ -1,0 +1,288 @@
+// C-ABI entry points of the SpMM plug-in (replaces SPMM_ACCEL,
+// spmm_accel.cu:104-139) and of the host-buffer call.
+#include "host_common.h"
+#include "kernels/spmm_kernels.cuh"
+
+#include <new>
+
+struct agcn_spmm_plan {
+    const int4 *block4 = nullptr;     // borrowed
+    int64_t n_blocks = 0, n_units = 0, n_rows = 0, n_cols = 0, nnz = 0;
+    int2 *unit_carry = nullptr;       // [n_units]
+    int *carry_row = nullptr;         // [n_carry]
+    float *carry = nullptr;           // [n_carry][SPMM_PANEL]
+    int *zero_rows = nullptr;         // [n_zero]
+    int64_t n_carry = 0, n_zero = 0;
+    int launches_last_run = 0;
+};
+
+namespace agcn {
+
+static void plan_free(agcn_spmm_plan *p)
+{
+    if (p == nullptr) return;
+    cudaFree(p->unit_carry);
+    cudaFree(p->carry_row);
+    cudaFree(p->carry);
+    cudaFree(p->zero_rows);
+    delete p;
+}
+
+static int spmm_create(agcn_spmm_plan **out, const int *d_block4, int64_t n_blocks, const int *d_indices,
+                       int64_t n_rows, int64_t n_cols, int64_t nnz, cudaStream_t s)
+{
+    AGCN_REQUIRE(out != nullptr, "agcn_spmm_create: null plan pointer");
+    *out = nullptr;
+    AGCN_REQUIRE(n_blocks >= 0 && (n_blocks == 0 || d_block4 != nullptr), "agcn_spmm_create: null block4");
+    AGCN_REQUIRE(aligned16(d_block4), "agcn_spmm_create: block4 must be 16-byte aligned");
+    AGCN_REQUIRE(n_rows > 0 && n_rows < (int64_t)INT32_MAX && n_cols > 0 && n_cols < (int64_t)INT32_MAX,
+                 "agcn_spmm_create: n_rows / n_cols out of range");
+    AGCN_REQUIRE(nnz >= 0 && nnz <= (int64_t)INT32_MAX, "agcn_spmm_create: nnz out of range");
+    AGCN_REQUIRE(n_blocks < (int64_t)INT32_MAX, "agcn_spmm_create: too many blocks");
+
+    const int4 *block4 = reinterpret_cast<const int4 *>(d_block4);
+    const int64_t n_units = ceil_div(n_blocks, SPMM_WARPS);
+    DeviceScratch scratch;
+    AGCN_ALLOC(gap, scratch, int, n_blocks + 1);
+    AGCN_ALLOC(gap_offset, scratch, int64_t, n_blocks + 1);
+    AGCN_ALLOC(cnt, scratch, int, n_units);
+    AGCN_ALLOC(slot_offset, scratch, int64_t, n_units);
+    AGCN_ALLOC(tile_sums, scratch, int64_t, scan_tiles(n_blocks + 1));
+    AGCN_ALLOC(d_res, scratch, int64_t, 3);    // [0] zero rows, [1] carry slots, [2] error bits (low int)
+    AGCN_CUDA(cudaMemsetAsync(d_res, 0, 3 * sizeof(int64_t), s));
+    int *d_err = reinterpret_cast<int *>(d_res + 2);
+
+    AGCN_KERNEL(plan_check_kernel, (unsigned)ceil_div(n_blocks + 1, 256), 256, s, block4, n_blocks, n_rows, nnz, gap, d_err);
+    AGCN_LAUNCH_CHECK("plan_check_kernel");
+    if (d_indices != nullptr && nnz > 0) {
+        const int64_t blocks = ceil_div(nnz, 256 * 16);
+        AGCN_KERNEL(plan_check_cols_kernel, (unsigned)(blocks < 65535 ? blocks : 65535), 256, s, d_indices, nnz, n_cols, d_err);
+        AGCN_LAUNCH_CHECK("plan_check_cols_kernel");
+    }
+    int rc = exclusive_scan_i32_i64(gap, gap_offset, n_blocks + 1, tile_sums, d_res + 0, s);
+    if (rc != AGCN_OK) return rc;
+    if (n_units > 0) {
+        AGCN_KERNEL(plan_count_carry_kernel, (unsigned)ceil_div(n_units, 256), 256, s, block4, n_blocks, n_units, cnt);
+        AGCN_LAUNCH_CHECK("plan_count_carry_kernel");
+        rc = exclusive_scan_i32_i64(cnt, slot_offset, n_units, tile_sums, d_res + 1, s);
+        if (rc != AGCN_OK) return rc;
+    }
+    int64_t res[3] = {0, 0, 0};
+    AGCN_CUDA(cudaMemcpyAsync(res, d_res, sizeof(res), cudaMemcpyDeviceToHost, s));
+    AGCN_CUDA(cudaStreamSynchronize(s));
+    const int err = (int)(res[2] & 0xffffffff);
+    if (err != 0) {
+        set_error("agcn_spmm_create: invalid input:%s%s%s%s",
+                  (err & SPMM_ERR_TUPLE) ? " malformed .block4 tuple;" : "",
+                  (err & SPMM_ERR_ROW) ? " tuple rows out of range or not ascending;" : "",
+                  (err & SPMM_ERR_LOC) ? " tuple nonzero range outside [0, nnz);" : "",
+                  (err & SPMM_ERR_COL) ? " column index outside [0, n_cols);" : "");
+        return AGCN_ERR_RANGE;
+    }
+
+    agcn_spmm_plan *p = new (std::nothrow) agcn_spmm_plan;
+    AGCN_REQUIRE(p != nullptr, "agcn_spmm_create: out of host memory");
+    p->block4 = block4; p->n_blocks = n_blocks; p->n_units = n_units;
+    p->n_rows = n_rows; p->n_cols = n_cols; p->nnz = nnz;
+    p->n_zero = res[0]; p->n_carry = res[1];
+    cudaError_t e = cudaSuccess;
+    if (e == cudaSuccess && n_units > 0) e = cudaMalloc(&p->unit_carry, (size_t)n_units * sizeof(int2));
+    if (e == cudaSuccess && p->n_carry > 0) e = cudaMalloc(&p->carry_row, (size_t)p->n_carry * sizeof(int));
+    if (e == cudaSuccess && p->n_carry > 0) e = cudaMalloc(&p->carry, (size_t)p->n_carry * SPMM_PANEL * sizeof(float));
+    if (e == cudaSuccess && p->n_zero > 0) e = cudaMalloc(&p->zero_rows, (size_t)p->n_zero * sizeof(int));
+    if (e != cudaSuccess) {
+        set_error("agcn_spmm_create: cudaMalloc of plan scratch: %s", cudaGetErrorString(e));
+        plan_free(p);
+        return AGCN_ERR_CUDA;
+    }
+    if (p->n_zero > 0)
+        AGCN_KERNEL(plan_zero_rows_kernel, (unsigned)ceil_div(n_blocks + 1, 256), 256, s, block4, n_blocks, (const int *)gap,
+                    (const int64_t *)gap_offset, p->zero_rows);
+    if (n_units > 0)
+        AGCN_KERNEL(plan_assign_carry_kernel, (unsigned)ceil_div(n_units, 256), 256, s, block4, n_blocks, n_units,
+                    (const int64_t *)slot_offset, p->unit_carry, p->carry_row);
+    e = cudaGetLastError();
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    if (e != cudaSuccess) {
+        set_error("agcn_spmm_create: plan kernels: %s", cudaGetErrorString(e));
+        plan_free(p);
+        return AGCN_ERR_CUDA;
+    }
+    *out = p;
+    return AGCN_OK;
+}
+
+template <int S>
+static void launch_units(const SpmmParams &prm, unsigned grid, cudaStream_t s)
+{
+    auto k = spmm_units_kernel<S>;
+    AGCN_KERNEL(k, grid, SPMM_THREADS, s, prm);
+}
+
+static int spmm_run(agcn_spmm_plan *p, const int *d_indices, const float *d_vals, const float *d_x, int64_t ldx,
+                    float *d_y, int64_t ldy, int dim, cudaStream_t s)
+{
+    AGCN_REQUIRE(p != nullptr, "agcn_spmm_run: null plan");
+    AGCN_REQUIRE(d_x != nullptr && d_y != nullptr, "agcn_spmm_run: null X or Y");
+    AGCN_REQUIRE(p->nnz == 0 || (d_indices != nullptr && d_vals != nullptr), "agcn_spmm_run: null indices or values");
+    AGCN_REQUIRE(dim >= 1, "agcn_spmm_run: dim = %d", dim);
+    AGCN_REQUIRE(ldx >= dim && ldy >= dim, "agcn_spmm_run: row stride smaller than dim");
+    p->launches_last_run = 0;
+    const int64_t zero_blocks = ceil_div(p->n_zero, SPMM_ZERO_ROWS_PER_BLOCK);
+    const int64_t grid = p->n_units + zero_blocks;
+    AGCN_REQUIRE(grid < (int64_t)INT32_MAX, "agcn_spmm_run: grid too large");
+    for (int col0 = 0; col0 < dim; col0 += SPMM_PANEL) {
+        const int width = dim - col0 < SPMM_PANEL ? dim - col0 : SPMM_PANEL;
+        SpmmParams prm;
+        prm.block4 = p->block4; prm.n_blocks = p->n_blocks; prm.n_units = p->n_units;
+        prm.idx = d_indices; prm.val = d_vals;
+        prm.x = d_x + col0; prm.ldx = ldx;
+        prm.y = d_y + col0; prm.ldy = ldy;
+        prm.dim = width;
+        prm.unit_carry = p->unit_carry; prm.carry = p->carry;
+        prm.zero_rows = p->zero_rows; prm.n_zero_rows = p->n_zero;
+        const bool vec = width % 4 == 0 && ldx % 4 == 0 && ldy % 4 == 0 && aligned16(prm.x) && aligned16(prm.y);
+        if (grid > 0) {
+            if (!vec) launch_units<0>(prm, (unsigned)grid, s);
+            else if (width <= 16) launch_units<4>(prm, (unsigned)grid, s);
+            else if (width <= 32) launch_units<8>(prm, (unsigned)grid, s);
+            else if (width <= 64) launch_units<16>(prm, (unsigned)grid, s);
+            else launch_units<32>(prm, (unsigned)grid, s);
+            AGCN_LAUNCH_CHECK("spmm_units_kernel");
+            p->launches_last_run++;
+        }
+        if (p->n_carry > 0) {
+            const unsigned cgrid = (unsigned)ceil_div(p->n_carry, SPMM_WARPS);
+            auto k = vec ? spmm_carry_kernel<true> : spmm_carry_kernel<false>;
+            AGCN_KERNEL(k, cgrid, SPMM_THREADS, s, (const float *)p->carry, (const int *)p->carry_row, p->n_carry, prm.y, ldy, width);
+            AGCN_LAUNCH_CHECK("spmm_carry_kernel");
+            p->launches_last_run++;
+        }
+    }
+    return AGCN_OK;
+}
+
+}  // namespace agcn
+
+extern "C" int agcn_spmm_create(agcn_spmm_plan **plan, const int32_t *d_block4, int64_t n_blocks,
+                                const int32_t *d_indices, int64_t n_rows, int64_t n_cols, int64_t nnz, void *stream)
+{
+    agcn::clear_error();
+    return agcn::spmm_create(plan, d_block4, n_blocks, d_indices, n_rows, n_cols, nnz, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int agcn_spmm_run(agcn_spmm_plan *plan, const int32_t *d_indices, const float *d_vals,
+                             const float *d_x, int64_t ldx, float *d_y, int64_t ldy, int dim, void *stream)
+{
+    agcn::clear_error();
+    return agcn::spmm_run(plan, d_indices, d_vals, d_x, ldx, d_y, ldy, dim, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int agcn_spmm_destroy(agcn_spmm_plan *plan)
+{
+    agcn::clear_error();
+    agcn::plan_free(plan);
+    return AGCN_OK;
+}
+
+extern "C" int agcn_spmm_plan_info(const agcn_spmm_plan *plan, int64_t *n_units, int64_t *n_carry,
+                                   int64_t *n_zero_rows, int *launches_last_run)
+{
+    agcn::clear_error();
+    AGCN_REQUIRE(plan != nullptr, "agcn_spmm_plan_info: null plan");
+    if (n_units) *n_units = plan->n_units;
+    if (n_carry) *n_carry = plan->n_carry;
+    if (n_zero_rows) *n_zero_rows = plan->n_zero;
+    if (launches_last_run) *launches_last_run = plan->launches_last_run;
+    return AGCN_OK;
+}
+
+// ---------------------------------------------------------------------------
+// host-buffer call
+// ---------------------------------------------------------------------------
+struct agcn_host_ctx {
+    cudaStream_t stream = nullptr;
+    void *buf[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};   // block4, idx, val, x, y
+    size_t cap[5] = {0, 0, 0, 0, 0};
+};
+
+namespace agcn {
+static int ctx_reserve(agcn_host_ctx *c, int which, size_t bytes)
+{
+    if (bytes <= c->cap[which]) return AGCN_OK;
+    if (c->buf[which] != nullptr) AGCN_CUDA(cudaFree(c->buf[which]));
+    c->buf[which] = nullptr; c->cap[which] = 0;
+    AGCN_CUDA(cudaMalloc(&c->buf[which], bytes));
+    c->cap[which] = bytes;
+    return AGCN_OK;
+}
+}  // namespace agcn
+
+extern "C" int agcn_host_ctx_create(agcn_host_ctx **ctx)
+{
+    using namespace agcn;
+    clear_error();
+    AGCN_REQUIRE(ctx != nullptr, "agcn_host_ctx_create: null pointer");
+    *ctx = nullptr;
+    agcn_host_ctx *c = new (std::nothrow) agcn_host_ctx;
+    AGCN_REQUIRE(c != nullptr, "agcn_host_ctx_create: out of host memory");
+    cudaError_t e = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking);
+    if (e != cudaSuccess) {
+        set_error("agcn_host_ctx_create: cudaStreamCreate: %s", cudaGetErrorString(e));
+        delete c;
+        return AGCN_ERR_CUDA;
+    }
+    *ctx = c;
+    return AGCN_OK;
+}
+
+extern "C" int agcn_host_ctx_destroy(agcn_host_ctx *ctx)
+{
+    agcn::clear_error();
+    if (ctx == nullptr) return AGCN_OK;
+    for (int i = 0; i < 5; i++) cudaFree(ctx->buf[i]);
+    if (ctx->stream) cudaStreamDestroy(ctx->stream);
+    delete ctx;
+    return AGCN_OK;
+}
+
+extern "C" int agcn_spmm_host(agcn_host_ctx *ctx, const int32_t *h_block4, int64_t n_blocks,
+                              const int32_t *h_indices, const float *h_vals, const float *h_x, float *h_y,
+                              int64_t n_rows, int64_t n_cols, int64_t nnz, int dim)
+{
+    using namespace agcn;
+    clear_error();
+    AGCN_REQUIRE(ctx != nullptr, "agcn_spmm_host: null context");
+    AGCN_REQUIRE(h_x != nullptr && h_y != nullptr, "agcn_spmm_host: null X or Y");
+    AGCN_REQUIRE(n_blocks >= 0 && (n_blocks == 0 || h_block4 != nullptr), "agcn_spmm_host: null block4");
+    AGCN_REQUIRE(nnz >= 0 && (nnz == 0 || (h_indices != nullptr && h_vals != nullptr)), "agcn_spmm_host: null indices or values");
+    AGCN_REQUIRE(n_rows > 0 && n_cols > 0 && dim >= 1, "agcn_spmm_host: bad sizes");
+    const size_t bytes[5] = {(size_t)n_blocks * 16, (size_t)nnz * 4, (size_t)nnz * 4,
+                             (size_t)n_cols * dim * 4, (size_t)n_rows * dim * 4};
+    for (int i = 0; i < 5; i++) {
+        int rc = ctx_reserve(ctx, i, bytes[i] > 0 ? bytes[i] : 16);
+        if (rc != AGCN_OK) return rc;
+    }
+    cudaStream_t s = ctx->stream;
+    const void *src[4] = {h_block4, h_indices, h_vals, h_x};
+    for (int i = 0; i < 4; i++)
+        if (bytes[i] > 0) AGCN_CUDA(cudaMemcpyAsync(ctx->buf[i], src[i], bytes[i], cudaMemcpyHostToDevice, s));
+    agcn_spmm_plan *plan = nullptr;
+    int rc = spmm_create(&plan, static_cast<const int *>(ctx->buf[0]), n_blocks, static_cast<const int *>(ctx->buf[1]),
+                         n_rows, n_cols, nnz, s);
+    if (rc != AGCN_OK) return rc;
+    rc = spmm_run(plan, static_cast<const int *>(ctx->buf[1]), static_cast<const float *>(ctx->buf[2]),
+                  static_cast<const float *>(ctx->buf[3]), dim, static_cast<float *>(ctx->buf[4]), dim, dim, s);
+    if (rc == AGCN_OK) {
+        cudaError_t e = cudaMemcpyAsync(h_y, ctx->buf[4], bytes[4], cudaMemcpyDeviceToHost, s);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+        if (e != cudaSuccess) {
+            set_error("agcn_spmm_host: download of Y: %s", cudaGetErrorString(e));
+            rc = AGCN_ERR_CUDA;
+        }
+    } else {
+        cudaStreamSynchronize(s);
+    }
+    plan_free(plan);
+    return rc;
+}
