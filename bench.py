@@ -1,0 +1,414 @@
+"""Benchmark of the Accel-GCN SpMM hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfg2]
+
+One step = one pass of the SpMM over the workload's dense widths (config 2: dim 32, 64 and
+128 on the 250 000-node / ~1.2e8-nonzero heavy graph).  Prints ONE JSON line.
+
+  value     whole-job GFLOP/s (2 * nnz * dim per product) with everything resident in HBM
+  e2e       the same through the host-buffer C-ABI call: .block4, indices, values and X go up
+            from pinned host memory and Y comes back, every step, inside the timed region
+  roofline  compulsory HBM bytes of the widest product / its CUDA-event time, against the
+            measured copy bandwidth of this pool's B200s
+  cpu_baseline  the CPU restatement of the reference path (oracle) on a bounded row sample
+
+`--impl reference` times that CPU path alone, with all host threads, on the same workload.
+Under torchrun with N > 1 the matrix is row-sharded by nonzeros and every step all-gathers
+the dense operand (strong scaling: the total work is fixed).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+PKG = os.path.join(ROOT, "iccad-accel-gcn_b200")
+for _p in (ROOT, PKG):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import numpy as np   # noqa: E402
+
+WORKLOADS = {
+    # name: (config id, scale, dims)
+    "cfg2": (2, 1.0, (32, 64, 128)),
+    "cfg1": (1, 1.0, (60,)),
+    "cfg3": (3, 1.0, (64,)),
+    "cfg4": (4, 1.0, tuple(range(16, 129, 4))),
+    "cfg2-small": (2, 0.04, (32, 64, 128)),      # for quick checks of the script itself
+}
+METRIC, UNIT = "spmm_gflops", "GFLOP/s"
+FALLBACK_HBM_GBS = 6650.0
+
+
+def hbm_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as fh:
+            return float(json.load(fh)["hbm_gbs"]), "measured (MEASURED_PEAKS.json, copy read+write)"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback (earlier measurement on this pool)"
+
+
+def min_bytes(nnz, n_blocks, n_rows, n_cols, dim):
+    """Compulsory HBM traffic of one product: A once, .block4 once, X once, Y once."""
+    return 8 * nnz + 16 * n_blocks + 4 * dim * n_cols + 4 * dim * n_rows
+
+
+def workload_description(name, g_info, n, nnz, n_blocks, dims):
+    return {"workload": f"{name}: synthetic config {g_info['config']} graph, N={n}, nnz={nnz}, "
+                        f"max degree {g_info['max_degree']}, {n_blocks} .block4 tuples, "
+                        f"SpMM at dim {'/'.join(map(str, dims))} per step",
+            "dims": list(dims), "n": n, "nnz": nnz, "n_blocks": n_blocks,
+            "l2": "no flush: A (8 B per nonzero) is larger than L2 and is streamed by every product"}
+
+
+# ----------------------------------------------------------------------------------------
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples of one GPU while a region runs."""
+    FIELDS = ("uuid,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, uuid: str):
+        self.uuid = uuid
+        self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=self.file, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.file.flush()
+        self.file.seek(0)
+        rows = [[c.strip() for c in line.split(",")] for line in self.file if line.count(",") >= 7]
+        self.file.close()
+        os.unlink(self.file.name)
+        mine = [r for r in rows if self.uuid and self.uuid in r[0]] or rows
+        sm, mx, pw, reasons = [], [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for r in mine:
+            try:
+                sm.append(float(r[1])); mx.append(float(r[2])); pw.append(float(r[3]))
+            except ValueError:
+                continue
+            for nme, flag in zip(names, r[4:8]):
+                if flag == "Active":
+                    reasons.add(nme)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(pw) if pw else None, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ----------------------------------------------------------------------------------------
+def build_workload(name, dev):
+    """Synthetic graph -> degree sort -> (sorted CSR on `dev`, generator info).  On a CUDA device
+    the ordering is done by the library; on the CPU (reference arm without a GPU) by the oracle."""
+    import torch
+    from accelgcn import synth
+    cfg, scale, dims = WORKLOADS[name]
+    g = synth.make_config(cfg, dev, scale)
+    if torch.device(dev).type == "cuda":
+        from accelgcn import degree_sort
+        _perm, ip, ix, v = degree_sort.degree_sort_device(g.indptr, g.indices, g.vals, relabel_cols=True)
+    else:
+        from oracle import oracle
+        _perm, ip, ix, v = oracle.degree_sort(g.indptr.numpy(), g.indices.numpy(), g.vals.numpy(), True)
+        ip, ix, v = torch.from_numpy(ip), torch.from_numpy(ix), torch.from_numpy(v)
+    return g, ip, ix, v, dims
+
+
+def row_sample(ip_h, ix_h, v_h, stride):
+    """Every stride-th row of a host CSR matrix (degree-ordered, so a strided sample keeps the degree mix)."""
+    if stride <= 1:
+        return ip_h, ix_h, v_h
+    rows = np.arange(0, len(ip_h) - 1, stride)
+    deg = (ip_h[rows + 1] - ip_h[rows]).astype(np.int64)
+    sp = np.concatenate([[0], np.cumsum(deg)])
+    src = np.repeat(ip_h[rows].astype(np.int64) - sp[:-1], deg) + np.arange(sp[-1])
+    return sp.astype(np.int32), ix_h[src], v_h[src]
+
+
+def cpu_spmm_rate(ip_h, ix_h, v_h, xs, budget_s):
+    """Times the CPU restatement (oracle, fp32, all OpenMP threads) on a strided row sample sized to
+    take about budget_s seconds over all widths.  Returns (GFLOP/s, seconds, sample description, stride)."""
+    from oracle import oracle
+    n, nnz = len(ip_h) - 1, len(ix_h)
+    dsum = sum(x.shape[1] for x in xs)
+    probe_stride = max(1, n // 2048)
+    sp, si, sv = row_sample(ip_h, ix_h, v_h, probe_stride)
+    oracle.spmm_csr(sp, si, sv, xs[0], f32_accumulate=True)                  # warm the threads
+    t0 = time.perf_counter()
+    for x in xs:
+        oracle.spmm_csr(sp, si, sv, x, f32_accumulate=True)
+    rate = 2.0 * len(si) * dsum / max(time.perf_counter() - t0, 1e-6)        # flop/s on the probe
+    want_nnz = rate * budget_s / (2.0 * dsum)
+    stride = max(1, int(np.ceil(nnz / max(want_nnz, 1.0))))
+    sp, si, sv = row_sample(ip_h, ix_h, v_h, stride)
+    t0 = time.perf_counter()
+    for x in xs:
+        oracle.spmm_csr(sp, si, sv, x, f32_accumulate=True)
+    dt = time.perf_counter() - t0
+    desc = (f"every {stride}th row of the degree-ordered matrix ({len(sp) - 1} rows, {len(si)} nonzeros), "
+            f"all widths, full X")
+    return 2.0 * len(si) * dsum / dt / 1e9, dt, desc, stride
+
+
+# ----------------------------------------------------------------------------------------
+def reference_arm(args, rank, world):
+    """The reference's CPU path for the SpMM (its only CPU code is the Python partitioner; the
+    product it is checked against is CSR x dense), restated in C with OpenMP in oracle/."""
+    if rank != 0:
+        return
+    import torch
+    from oracle import oracle
+    dev = "cuda:0" if torch.cuda.is_available() else "cpu"
+    g, ip, ix, v, dims = build_workload(args.workload, dev)
+    n, nnz = g.n, int(ix.numel())
+    ip_h, ix_h, v_h = ip.cpu().numpy(), ix.cpu().numpy(), v.cpu().numpy()
+    n_blocks = int(len(oracle.partition(ip_h)))
+    from accelgcn import synth
+    xs = [synth.features(n, d, g.info["seed"], "cpu").numpy() for d in dims]
+    del g, ip, ix, v
+    dsum = sum(dims)
+    per_step = min(2.0, 150.0 / max(args.steps + args.warmup, 1))
+    _rate, _dt, desc, stride = cpu_spmm_rate(ip_h, ix_h, v_h, xs, per_step)
+    sp, si, sv = row_sample(ip_h, ix_h, v_h, stride)
+    for _ in range(args.warmup):
+        for x in xs:
+            oracle.spmm_csr(sp, si, sv, x, f32_accumulate=True)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        for x in xs:
+            oracle.spmm_csr(sp, si, sv, x, f32_accumulate=True)
+    dt = time.perf_counter() - t0
+    gflops = 2.0 * len(si) * dsum * args.steps / dt / 1e9
+    info = {"config": WORKLOADS[args.workload][0], "max_degree": int(np.diff(ip_h).max())}
+    line = {"impl": "reference", "metric": METRIC, "value": gflops, "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": workload_description(args.workload, info, n, nnz, n_blocks, dims),
+            "cpu_baseline": {"value": gflops, "unit": UNIT, "cores": oracle.num_threads(), "kind": "port",
+                             "sample": "each step: " + desc},
+            "e2e": {"value": gflops, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------------------
+def ours(args, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+    from accelgcn import synth, sharded, spmm as spmm_mod, _lib
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device: the library has no CPU fallback"
+    _lib.load()
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+
+    def barrier():
+        torch.cuda.synchronize(dev)
+        if world > 1:
+            dist.barrier()
+
+    g, ip, ix, v, dims = build_workload(args.workload, dev)
+    n, nnz = g.n, int(ix.numel())
+    shard = sharded.ShardedSpmm(ip, ix, v, rank, world)
+    ip_full_h = ip.cpu().numpy() if rank == 0 else None
+    r0, r1 = shard.row_range
+    n_blocks_local = int(shard.block4.shape[0])
+    nb = torch.tensor([n_blocks_local], dtype=torch.int64, device=dev)
+    if world > 1:
+        dist.all_reduce(nb)
+    n_blocks = int(nb.item())
+    xs = {d: synth.features(n, d, g.info["seed"], dev)[r0:r1].contiguous() for d in dims}
+    ys = {d: torch.empty((r1 - r0, d), dtype=torch.float32, device=dev) for d in dims}
+    if world > 1:
+        del ip, ix, v
+    torch.cuda.empty_cache()
+
+    def step(record=None):
+        for di, d in enumerate(dims):
+            if record is not None:
+                record[di][0].record()
+            shard.step(xs[d], ys[d])
+            if record is not None:
+                record[di][1].record()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    launches_per_step = 0
+    for d in dims:
+        shard.step(xs[d], ys[d])
+        launches_per_step += shard.plan.info()["launches_last_run"]
+    barrier()
+
+    uuid = str(getattr(torch.cuda.get_device_properties(dev), "uuid", ""))
+    sampler = ClockSampler(uuid)
+    evs = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in dims]
+           for _ in range(args.steps)]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for k in range(args.steps):
+        step(evs[k])
+    e1.record()
+    barrier()
+    total_ms = e0.elapsed_time(e1)
+    # keep the same load running (untimed) until the clock sampler has seen about 1.5 s of it
+    t_load = time.perf_counter()
+    while total_ms < 1500 and time.perf_counter() - t_load < 1.5 - total_ms / 1e3:
+        step()
+        torch.cuda.synchronize(dev)
+    clocks = sampler.stop()
+    t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
+    per_dim_ms = torch.tensor([np.mean([evs[k][di][0].elapsed_time(evs[k][di][1]) for k in range(args.steps)])
+                               for di in range(len(dims))], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(per_dim_ms, op=dist.ReduceOp.MAX)
+    total_ms = float(t.item())
+    per_dim_ms = per_dim_ms.tolist()
+    flops_step = 2.0 * nnz * sum(dims)
+    value = flops_step * args.steps / (total_ms / 1e3) / 1e9
+
+    if args.kernel_only:
+        # profiling mode: the resident-data loop only (no end-to-end, CPU or reference legs)
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "value": value, "unit": UNIT, "steps": args.steps,
+                              "ms_per_step": total_ms / args.steps, "per_dim_ms": per_dim_ms, "kernel_only": True}))
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    # ---- end to end through the host-buffer C-ABI call, pinned host memory -------------------
+    host = spmm_mod.HostSpmm()
+    hb = {"b4": shard.block4.cpu().pin_memory(), "ix": shard.indices.cpu().pin_memory(),
+          "v": shard.vals.cpu().pin_memory()}
+    hx, hy = {}, {}
+    for d in dims:
+        full = synth.features(n, d, g.info["seed"], dev)
+        if world > 1:       # the host call takes the dense operand in the shard's padded numbering
+            full = sharded.all_gather_padded(full[r0:r1].contiguous(), shard.max_rows, world)
+        hx[d] = full.cpu().pin_memory()
+        hy[d] = torch.empty((r1 - r0, d), dtype=torch.float32).pin_memory()
+        del full
+    e2e_steps = max(1, min(args.steps, 5))
+
+    def e2e_step():
+        for d in dims:
+            host(hb["b4"], hb["ix"], hb["v"], hx[d], r1 - r0, out=hy[d])
+
+    e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    barrier()
+    e2e_s = torch.tensor([time.perf_counter() - t0], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(e2e_s, op=dist.ReduceOp.MAX)
+    e2e_value = flops_step * e2e_steps / float(e2e_s.item()) / 1e9
+    h2d = sum(16 * n_blocks_local + 8 * int(shard.indices.numel()) + 4 * d * int(hx[d].shape[0]) for d in dims)
+    d2h = sum(4 * d * (r1 - r0) for d in dims)
+    e2e_ok = bool(torch.equal(hy[dims[-1]], ys[dims[-1]].cpu()))     # same bits as the resident run
+    host.close()
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peak, peak_src = hbm_peak()
+    props = torch.cuda.get_device_properties(dev)
+    per_dim = []
+    for d, ms in zip(dims, per_dim_ms):
+        b = min_bytes(nnz, n_blocks, n, n, d)
+        per_dim.append({"dim": d, "ms": ms, "gflops": 2.0 * nnz * d / ms / 1e6, "hbm_gbs": b / ms / 1e6,
+                        "hbm_frac": b / ms / 1e6 / peak,
+                        "gather_gbs_l2_inclusive": (nnz * (8 + 4 * d) + 4 * d * n + 16 * n_blocks) / ms / 1e6})
+    top = max(per_dim, key=lambda r: r["ms"])
+    fp32_peak = props.multi_processor_count * 128 * 2 * (clocks["sm_mhz"] or clocks["sm_max_mhz"] or 1965.0) * 1e6
+    roofline = {"bound": "hbm", "achieved": top["hbm_gbs"], "peak": peak, "unit": "GB/s",
+                "frac": top["hbm_frac"], "traffic": None, "kernel": f"spmm_units_kernel dim={top['dim']}",
+                "peak_source": peak_src,
+                "algorithmic_bytes_per_launch": min_bytes(nnz, n_blocks, n, n, top["dim"]),
+                "fp32_frac_at_sampled_clock": 2.0 * nnz * top["dim"] / (top["ms"] / 1e3) / fp32_peak}
+    line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": total_ms / args.steps, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": workload_description(args.workload, g.info, n, nnz, n_blocks, dims),
+            "roofline": roofline, "per_dim": per_dim, "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "steps": e2e_steps, "bit_identical_to_resident_run": e2e_ok},
+            "gpu_launches": launches_per_step * args.steps,
+            "plan": shard.plan.info()}
+
+    if world == 1:
+        ip_h, ix_h, v_h = ip_full_h, ix.cpu().numpy(), v.cpu().numpy()
+        xs_h = [xs[d].cpu().numpy() for d in dims]
+        if not args.no_ref_gpu:
+            line["reference_gpu"] = reference_gpu_kernels(shard.block4.cpu().numpy(), ip_h, ix_h, v_h, xs_h, dims, nnz)
+        from oracle import oracle
+        gf, dt, desc, _ = cpu_spmm_rate(ip_h, ix_h, v_h, xs_h, args.cpu_seconds)
+        line["cpu_baseline"] = {"value": gf, "unit": UNIT, "cores": oracle.num_threads(), "kind": "port",
+                                "sample": desc, "seconds": dt}
+    else:
+        dist.destroy_process_group()
+    print(json.dumps(line), flush=True)
+
+
+def reference_gpu_kernels(block4, ip_h, ix_h, v_h, xs_h, dims, nnz):
+    """The reference's own spmm_accel kernel and its cuSPARSE call, compiled from the reference
+    sources (oracle/_ref), timed on this GPU with the reference's own protocol (mean wall-clock
+    seconds of 4 resp. 10 launches after as many warm-ups)."""
+    from oracle import oracle
+    if not oracle.ref_available():
+        return {"unavailable": "oracle/_ref/libref_accel.so not built (needs the reference tree at build time)"}
+    out = {}
+    for x, d in zip(xs_h, dims):
+        if (len(ip_h) - 1) * d >= 2**31 or d > 128:
+            out[str(d)] = {"unavailable": "outside the reference kernel's int32 / dim <= 128 limits"}
+            continue
+        ta = oracle.ref_accel_spmm(block4, ip_h, ix_h, v_h, x, timing=True)
+        tc = oracle.ref_cusparse_spmm(ip_h, ix_h, v_h, x, timing=True)
+        out[str(d)] = {"accel_ms": ta * 1e3, "accel_gflops": 2.0 * nnz * d / ta / 1e9,
+                       "cusparse_ms": tc * 1e3, "cusparse_gflops": 2.0 * nnz * d / tc / 1e9}
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS), default="cfg2")
+    ap.add_argument("--cpu-seconds", type=float, default=15.0, help="CPU time spent on the cpu_baseline sample")
+    ap.add_argument("--no-ref-gpu", action="store_true", help="skip timing the reference's GPU kernels")
+    ap.add_argument("--kernel-only", action="store_true", help="resident-data loop only (for profiling under ncu)")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        reference_arm(args, rank, world)
+    else:
+        ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

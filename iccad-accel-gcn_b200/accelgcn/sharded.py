@@ -1,0 +1,123 @@
+"""1D row-sharded multi-GPU SpMM: one process per GPU, torch.distributed for the
+exchange, libaccelgcn.so for every kernel.
+
+The degree-ordered matrix A is cut at row boundaries into one contiguous row
+range per rank, balanced by nonzeros (not rows).  Each rank keeps its rows of
+A, its own `.block4` metadata (the partitioner run on the shard's row
+pointers -- the format is unchanged, row and nonzero offsets are shard-local)
+and the same rows of the dense operand.  One step is: all-gather the dense
+operand (the only exchange the path has), then the local SpMM.
+
+All ranks' dense rows are gathered into one padded buffer of
+world_size * max_rows rows, so the collective is a single equal-sized
+all-gather even though the shards hold different numbers of rows; the column
+ids of each shard are renumbered once, at set-up, to positions in that buffer.
+
+The reference has no multi-GPU code; this follows its single-GPU operator
+(spmm_accel.cu) shard by shard.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+
+def nnz_balanced_cuts(indptr, n_parts: int) -> np.ndarray:
+    """Row cut points c[0]=0 <= ... <= c[n_parts]=n_rows such that every range
+    [c[k], c[k+1]) holds about nnz / n_parts nonzeros.  Cuts fall on row
+    boundaries (a row is never split); indptr is a host array."""
+    indptr = np.asarray(indptr, dtype=np.int64)
+    n_rows = len(indptr) - 1
+    nnz = int(indptr[-1] - indptr[0])
+    targets = indptr[0] + (np.arange(1, n_parts, dtype=np.int64) * nnz) // n_parts
+    inner = np.searchsorted(indptr, targets, side="left")
+    cuts = np.concatenate([[0], np.clip(inner, 0, n_rows), [n_rows]]).astype(np.int64)
+    return np.maximum.accumulate(cuts)
+
+
+def padded_position(cols, cuts, max_rows: int):
+    """Global row id -> row of the padded all-gather buffer (rank * max_rows + local row).
+    Works on numpy arrays and torch tensors alike."""
+    is_np = isinstance(cols, np.ndarray)
+    if is_np:
+        owner = np.searchsorted(cuts[1:-1], cols, side="right")
+        return (owner * max_rows + (cols - np.asarray(cuts)[owner])).astype(cols.dtype)
+    import torch
+    c = torch.as_tensor(np.asarray(cuts), device=cols.device)
+    owner = torch.searchsorted(c[1:-1].contiguous(), cols.to(torch.int64), right=True)
+    return (owner * max_rows + (cols.to(torch.int64) - c[owner])).to(cols.dtype)
+
+
+def shard_rows(indptr, indices, vals, cuts, rank: int):
+    """The rows [cuts[rank], cuts[rank+1]) of a CSR matrix, row pointers rebased to 0."""
+    r0, r1 = int(cuts[rank]), int(cuts[rank + 1])
+    p0, p1 = int(indptr[r0]), int(indptr[r1])
+    return indptr[r0:r1 + 1] - indptr[r0], indices[p0:p1], vals[p0:p1]
+
+
+def all_gather_padded(x_local, max_rows: int, world_size: int, out=None, group=None):
+    """All-gather the ranks' row blocks (each at most max_rows rows) into one
+    [world_size * max_rows, dim] buffer.  Rows past a rank's own count are
+    padding and are never referenced by a renumbered column id."""
+    import torch
+    import torch.distributed as dist
+    dim = x_local.shape[1]
+    if out is None:
+        out = torch.empty((world_size * max_rows, dim), dtype=x_local.dtype, device=x_local.device)
+    if x_local.shape[0] == max_rows and x_local.is_contiguous():
+        send = x_local
+    else:
+        send = torch.zeros((max_rows, dim), dtype=x_local.dtype, device=x_local.device)
+        send[: x_local.shape[0]] = x_local
+    if world_size == 1:
+        out.copy_(send)
+    else:
+        dist.all_gather_into_tensor(out, send, group=group)
+    return out
+
+
+class ShardedSpmm:
+    """This rank's shard of a degree-ordered A, ready to multiply.
+
+    indptr / indices / vals are the FULL degree-ordered matrix as CUDA tensors
+    on this rank's device (every rank builds the same synthetic matrix from the
+    same seed, or loads the same files); the shard is cut out here."""
+
+    def __init__(self, indptr, indices, vals, rank: int, world_size: int, group=None):
+        import torch
+        from . import partition, spmm
+        self.rank, self.world, self.group = rank, world_size, group
+        self.n = indptr.numel() - 1
+        self.cuts = nnz_balanced_cuts(indptr.cpu().numpy(), world_size)
+        self.max_rows = int(np.diff(self.cuts).max())
+        ip, ix, v = shard_rows(indptr, indices, vals, self.cuts, rank)
+        self.indptr = ip.contiguous()
+        self.vals = v.contiguous()
+        self.indices = padded_position(ix.contiguous(), self.cuts, self.max_rows) if world_size > 1 else ix.contiguous()
+        self.n_local = self.indptr.numel() - 1
+        self.n_cols = world_size * self.max_rows if world_size > 1 else self.n
+        self.block4 = partition.block_level_partition_device(self.indptr)
+        self.plan = spmm.SpmmPlan(self.block4, self.indices, self.n_local, self.n_cols)
+        self._gather = {}
+        self.device = indptr.device
+        self._torch = torch
+
+    @property
+    def row_range(self):
+        return int(self.cuts[self.rank]), int(self.cuts[self.rank + 1])
+
+    def step(self, x_local, y_local):
+        """y_local[n_local x dim] = A_shard @ allgather(x_local).  Asynchronous on the current stream."""
+        dim = x_local.shape[1]
+        if self.world == 1:
+            x_full = x_local
+        else:
+            buf = self._gather.get(dim)
+            if buf is None:
+                buf = self._torch.empty((self.n_cols, dim), dtype=x_local.dtype, device=self.device)
+                self._gather[dim] = buf
+            x_full = all_gather_padded(x_local, self.max_rows, self.world, out=buf, group=self.group)
+        self.plan.run(self.indices, self.vals, x_full, y_local, dim=dim, ldx=dim, ldy=dim)
+        return y_local
+
+    def close(self):
+        self.plan.close()

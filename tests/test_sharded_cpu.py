@@ -1,0 +1,91 @@
+"""Host-side logic of the row-sharded path on CPU: nnz-balanced cuts, column renumbering and
+the padded all-gather over the gloo backend with two ranks.  The arithmetic of a shard is
+checked with the CPU oracle here; the GPU kernels are covered by the -m gpu tests."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from conftest import spmm_close
+from oracle import oracle
+
+
+def _graph(n=700, seed=0):
+    rng = np.random.default_rng(seed)
+    deg = np.sort(np.minimum((rng.pareto(1.0, n) * 3).astype(np.int64), n // 2))
+    indptr = np.concatenate([[0], np.cumsum(deg)]).astype(np.int32)
+    idx = np.concatenate([np.sort(rng.choice(n, d, replace=False)) for d in deg]).astype(np.int32)
+    val = rng.random(len(idx)).astype(np.float32)
+    return indptr, idx, val
+
+
+def test_cuts_balance_nonzeros_not_rows():
+    from accelgcn import sharded
+    indptr, _, _ = _graph(5000, 1)
+    for parts in (1, 2, 4, 8):
+        cuts = sharded.nnz_balanced_cuts(indptr, parts)
+        assert cuts[0] == 0 and cuts[-1] == 5000 and np.all(np.diff(cuts) >= 0) and len(cuts) == parts + 1
+        per = np.diff(indptr[cuts].astype(np.int64))
+        assert per.sum() == indptr[-1]
+        if parts > 1:
+            assert per.max() - per.min() <= 2 * np.diff(indptr).max()          # within one (heaviest) row
+            assert np.diff(cuts).max() > 2 * np.diff(cuts).min()                # rows are NOT balanced
+
+
+def test_cuts_degenerate_inputs():
+    from accelgcn import sharded
+    assert sharded.nnz_balanced_cuts(np.zeros(5, dtype=np.int32), 4).tolist() == [0, 0, 0, 0, 4]
+    assert sharded.nnz_balanced_cuts(np.array([0, 10]), 3).tolist()[-1] == 1
+
+
+def test_padded_position_is_consistent_with_the_gather_layout():
+    from accelgcn import sharded
+    cuts = np.array([0, 5, 6, 20])
+    max_rows = 14
+    cols = np.arange(20, dtype=np.int32)
+    pos = sharded.padded_position(cols, cuts, max_rows)
+    assert pos[:5].tolist() == [0, 1, 2, 3, 4] and pos[5] == 14 and pos[6] == 28 and pos[19] == 41
+    pos_t = sharded.padded_position(torch.from_numpy(cols), cuts, max_rows)
+    assert pos_t.dtype == torch.int32 and pos_t.tolist() == pos.tolist()
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, dim, result_dir):
+    from accelgcn import sharded
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        indptr, idx, val = _graph()
+        n = len(indptr) - 1
+        x = np.random.default_rng(7).uniform(-1, 1, (n, dim)).astype(np.float32)
+        cuts = sharded.nnz_balanced_cuts(indptr, world)
+        max_rows = int(np.diff(cuts).max())
+        ip, ix, v = sharded.shard_rows(indptr, idx, val, cuts, rank)
+        ix = sharded.padded_position(ix, cuts, max_rows)
+        r0, r1 = int(cuts[rank]), int(cuts[rank + 1])
+        x_full = sharded.all_gather_padded(torch.from_numpy(x[r0:r1]), max_rows, world).numpy()
+        # the shard's own .block4 and product, computed by the oracle (this is a CPU test)
+        y = oracle.spmm_block4(oracle.partition(ip), ix, v, x_full, r1 - r0)
+        np.save(os.path.join(result_dir, f"y{rank}.npy"), y)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_two_rank_gloo_sharded_product_equals_single_rank(world, tmp_path):
+    dim = 12
+    mp.spawn(_worker, args=(world, _free_port(), dim, str(tmp_path)), nprocs=world, join=True)
+    indptr, idx, val = _graph()
+    x = np.random.default_rng(7).uniform(-1, 1, (len(indptr) - 1, dim)).astype(np.float32)
+    ref = oracle.spmm_csr(indptr, idx, val, x)
+    y = np.concatenate([np.load(tmp_path / f"y{r}.npy") for r in range(world)])
+    assert y.shape == ref.shape and spmm_close(y, ref, np.full(len(ref), 50.0)).all()

@@ -1,0 +1,224 @@
+"""Parity of the GPU SpMM with the oracle (CSR x dense in fp64, and the thread-for-thread fp32
+restatement of the reference kernel), through the C ABI.  Tolerance: rel 1e-4 / abs 1e-5."""
+import os
+
+import numpy as np
+import pytest
+
+from conftest import require_cuda, spmm_close, row_abs_scale
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+class Case:
+    """A degree-ordered synthetic graph on host and device with its .block4 metadata."""
+
+    def __init__(self, cfg, scale, sort=True, empty_rows=()):
+        import torch
+        from accelgcn import synth, degree_sort, partition
+        self.dev = require_cuda()
+        g = synth.make_config(cfg, "cpu", scale)
+        ip, ix, v = g.indptr.numpy(), g.indices.numpy(), g.vals.numpy()
+        if len(empty_rows):                       # drop every nonzero of the named rows
+            deg = np.diff(ip.astype(np.int64))
+            keep = np.ones(len(ix), dtype=bool)
+            for r in empty_rows:
+                keep[ip[r]:ip[r + 1]] = False
+                deg[r] = 0
+            ix, v = ix[keep], v[keep]
+            ip = np.concatenate([[0], np.cumsum(deg)]).astype(np.int32)
+        if sort:
+            _, ip, ix, v = degree_sort.degree_sort(ip, ix, v, relabel_cols=True)
+        self.n, self.indptr, self.idx, self.val = g.n, ip, ix, v
+        self.block4 = partition.block_level_partition(ip)
+        self.seed = g.info["seed"]
+        self.t = {k: torch.from_numpy(a).to(self.dev) for k, a in
+                  (("block4", self.block4), ("idx", ix), ("val", v))}
+
+    def x(self, dim):
+        from accelgcn import synth
+        return synth.features(self.n, dim, self.seed, "cpu").numpy()
+
+    def run(self, x, prefill=float("nan")):
+        import torch
+        from accelgcn import spmm
+        xt = torch.from_numpy(x).to(self.dev)
+        y = torch.full((self.n, x.shape[1]), prefill, dtype=torch.float32, device=self.dev)
+        spmm.spmm(self.t["block4"], self.t["idx"], self.t["val"], xt, self.n, out=y)
+        return y.cpu().numpy()
+
+    def check(self, x, y):
+        ref = oracle.spmm_csr(self.indptr, self.idx, self.val, x)
+        ok = spmm_close(y, ref, row_abs_scale(self.indptr, self.val, x))
+        assert not np.isnan(y).any(), "some of Y was not written"
+        assert ok.all(), f"{(~ok).sum()} elements out of tolerance, first at {np.argwhere(~ok)[0]}"
+
+
+@pytest.fixture(scope="module")
+def cfg1():
+    return Case(1, 1.0)
+
+
+@pytest.fixture(scope="module")
+def cfg4_small():
+    return Case(4, 0.04)      # 20 000 rows, one row of 8 000 nonzeros: heavy rows crossing units
+
+
+@pytest.mark.parametrize("dim", list(range(16, 129, 4)) + [1, 7, 17, 33, 61, 99, 127])
+def test_config1_every_dim_against_oracle(cfg1, dim):
+    x = cfg1.x(dim)
+    cfg1.check(x, cfg1.run(x))
+
+
+@pytest.mark.parametrize("dim", [16, 32, 60, 64, 100, 128, 45])
+def test_skewed_graph_heavy_rows(cfg4_small, dim):
+    x = cfg4_small.x(dim)
+    y = cfg4_small.run(x)
+    cfg4_small.check(x, y)
+
+
+def test_matches_reference_kernel_restatement_in_fp32(cfg1):
+    # against the thread-for-thread fp32 model of spmm_accel.cu on a zeroed Y
+    x = cfg1.x(60)
+    y = cfg1.run(x)
+    ref32 = oracle.spmm_block4(cfg1.block4, cfg1.idx, cfg1.val, x, cfg1.n)
+    assert spmm_close(y, ref32, row_abs_scale(cfg1.indptr, cfg1.val, x)).all()
+
+
+@pytest.mark.parametrize("cfg,scale,dim", [(2, 0.02, 64), (3, 0.02, 64), (5, 0.002, 128)])
+def test_other_configs_scaled_down(cfg, scale, dim):
+    c = Case(cfg, scale)
+    x = c.x(dim)
+    c.check(x, c.run(x))
+
+
+def test_overwrites_output_and_is_bitwise_reproducible(cfg4_small):
+    x = cfg4_small.x(64)
+    a = cfg4_small.run(x, prefill=float("nan"))
+    b = cfg4_small.run(x, prefill=123.0)
+    c = cfg4_small.run(x, prefill=-1e30)
+    assert np.array_equal(a, b) and np.array_equal(a, c)
+
+
+def test_unsorted_rows_and_zero_degree_rows_anywhere():
+    # .block4 of an unsorted graph (zero-degree rows in the middle and at the end)
+    n = 12_000
+    c = Case(3, 0.005, sort=False, empty_rows=(0, 1, 2, 77, 78, 5000, n - 2, n - 1))
+    assert c.n == n and (np.diff(c.indptr) == 0).sum() >= 8 and (np.diff(np.diff(c.indptr)) < 0).any()
+    for dim in (32, 60, 9):
+        x = c.x(dim)
+        c.check(x, c.run(x))
+
+
+def test_wide_and_strided_operands(cfg1):
+    import torch
+    from accelgcn import spmm
+    dev = cfg1.dev
+    # dim > 128 is processed in 128-column panels; ld > dim exercises the row strides
+    x = cfg1.x(200)
+    cfg1.check(x, cfg1.run(x))
+    xw = torch.from_numpy(cfg1.x(96)).to(dev)
+    ybuf = torch.full((cfg1.n, 128), float("nan"), dtype=torch.float32, device=dev)
+    plan = spmm.SpmmPlan(cfg1.t["block4"], cfg1.t["idx"], cfg1.n, cfg1.n)
+    plan.run(cfg1.t["idx"], cfg1.t["val"], xw[:, :64], ybuf[:, 32:96], dim=64, ldx=96, ldy=128)
+    torch.cuda.synchronize()
+    plan.close()
+    out = ybuf.cpu().numpy()
+    cfg1.check(xw[:, :64].cpu().numpy().copy(), out[:, 32:96].copy())
+    assert np.isnan(out[:, :32]).all() and np.isnan(out[:, 96:]).all()       # nothing outside the panel touched
+
+
+def test_linearity_at_full_size_config3_shape():
+    # property that needs no oracle at a size the CPU cannot check quickly: A(ax + by) = aAx + bAy
+    import torch
+    from accelgcn import synth, degree_sort, partition, spmm
+    dev = require_cuda()
+    g = synth.make_config(3, dev, 0.25)          # 600 000 rows, ~15 M nonzeros
+    _, ip, ix, v = degree_sort.degree_sort_device(g.indptr, g.indices, g.vals, relabel_cols=True)
+    b4 = partition.block_level_partition_device(ip)
+    x1 = synth.features(g.n, 64, 1, dev)
+    x2 = synth.features(g.n, 64, 2, dev)
+    y1 = spmm.spmm(b4, ix, v, x1, g.n)
+    y2 = spmm.spmm(b4, ix, v, x2, g.n)
+    y3 = spmm.spmm(b4, ix, v, 0.5 * x1 - 2.0 * x2, g.n)
+    assert torch.allclose(y3, 0.5 * y1 - 2.0 * y2, rtol=1e-4, atol=1e-5)
+    # and a sampled-row check against the fp64 CSR product
+    rows = torch.randint(0, g.n, (300,), device=dev).tolist() + [g.n - 1]
+    ip_h, ix_h, v_h, x_h = ip.cpu().numpy(), ix.cpu().numpy(), v.cpu().numpy(), x1.cpu().numpy().astype(np.float64)
+    y_h = y1.cpu().numpy()
+    for r in rows:
+        s = slice(ip_h[r], ip_h[r + 1])
+        ref = (v_h[s].astype(np.float64)[:, None] * x_h[ix_h[s]]).sum(0)
+        assert np.all(np.abs(y_h[r] - ref) <= 1e-5 + 1e-4 * np.abs(ref)), r
+
+
+def test_host_buffer_entry_point(cfg1):
+    from accelgcn import spmm
+    h = spmm.HostSpmm()
+    for dim in (60, 128):
+        x = cfg1.x(dim)
+        y = h(cfg1.block4, cfg1.idx, cfg1.val, x, cfg1.n)
+        cfg1.check(x, y)
+    h.close()
+
+
+def test_plugin_class_mirrors_reference_do_test(cfg1, tmp_path):
+    # SPMM_ACCEL usage as in main.cu:131,146,166: buffers of dim_max columns, .block4 read from
+    # ../block_level_meta/<graph>.block4 on every do_test, vin/vout re-read per dim
+    import torch
+    from accelgcn import spmm, graphio
+    os.makedirs(tmp_path / "block_level_meta")
+    graphio.write_block4(str(tmp_path / "block_level_meta" / "g.block4"), cfg1.block4)
+    dev, n, dim_max = cfg1.dev, cfg1.n, 128
+    vin = torch.from_numpy(cfg1.x(dim_max)).to(dev).reshape(-1)
+    vout = torch.zeros(n * dim_max, dtype=torch.float32, device=dev)
+    accel = spmm.SpmmAccel("g", torch.from_numpy(cfg1.indptr).to(dev), cfg1.t["idx"], cfg1.t["val"], vin, vout,
+                           n, len(cfg1.idx), dim_max, meta_dir=str(tmp_path / "block_level_meta"))
+    for dim in (60, 128):
+        assert accel.do_test(False, dim) == 0.0
+        x = vin[: n * dim].reshape(n, dim).cpu().numpy()
+        cfg1.check(x, vout[: n * dim].reshape(n, dim).cpu().numpy())
+    assert accel.do_test(True, 64) > 0.0
+
+
+def test_invalid_input_is_rejected_not_faulted(cfg1):
+    import torch
+    from accelgcn import spmm, AccelGcnError
+    dev = cfg1.dev
+    bad_idx = cfg1.t["idx"].clone()
+    bad_idx[5] = cfg1.n + 3
+    with pytest.raises(AccelGcnError, match="column index"):
+        spmm.SpmmPlan(cfg1.t["block4"], bad_idx, cfg1.n, cfg1.n)
+    bad_b4 = cfg1.t["block4"].clone()
+    bad_b4[3, 2] = len(cfg1.idx)                      # loc_begin past the end
+    with pytest.raises(AccelGcnError, match="nonzero range"):
+        spmm.SpmmPlan(bad_b4, cfg1.t["idx"], cfg1.n, cfg1.n)
+    bad_b4 = cfg1.t["block4"].clone()
+    bad_b4[0, 1] = cfg1.n                             # row out of range
+    with pytest.raises(AccelGcnError, match="rows"):
+        spmm.SpmmPlan(bad_b4, cfg1.t["idx"], cfg1.n, cfg1.n)
+    torch.cuda.synchronize()
+
+
+@pytest.mark.skipif(not oracle.ref_available(), reason="oracle/_ref not built (needs the reference tree at build time)")
+@pytest.mark.parametrize("dim", [16, 60, 64, 100, 128])
+def test_parity_with_the_reference_kernel_itself(cfg1, dim):
+    # the reference's spmm_kernel_accel, compiled from its own sources for sm_100a, on a zeroed Y
+    x = cfg1.x(dim)
+    ref = oracle.ref_accel_spmm(cfg1.block4, cfg1.indptr, cfg1.idx, cfg1.val, x)
+    y = cfg1.run(x)
+    assert spmm_close(y, ref, row_abs_scale(cfg1.indptr, cfg1.val, x)).all()
+    # the C restatement of that kernel is pinned by the same run
+    model = oracle.spmm_block4(cfg1.block4, cfg1.idx, cfg1.val, x, cfg1.n)
+    assert spmm_close(model, ref, row_abs_scale(cfg1.indptr, cfg1.val, x)).all()
+
+
+@pytest.mark.skipif(not oracle.ref_available(), reason="oracle/_ref not built")
+def test_parity_with_the_reference_kernel_heavy_rows(cfg4_small):
+    x = cfg4_small.x(64)
+    ref = oracle.ref_accel_spmm(cfg4_small.block4, cfg4_small.indptr, cfg4_small.idx, cfg4_small.val, x)
+    y = cfg4_small.run(x)
+    assert spmm_close(y, ref, row_abs_scale(cfg4_small.indptr, cfg4_small.val, x)).all()
+    cs = oracle.ref_cusparse_spmm(cfg4_small.indptr, cfg4_small.idx, cfg4_small.val, x)
+    assert spmm_close(y, cs, row_abs_scale(cfg4_small.indptr, cfg4_small.val, x)).all()
