@@ -49,6 +49,7 @@ struct SpmmParams {
     float *carry;             // [n_carry][SPMM_PANEL]
     const int *zero_rows;     // rows no tuple covers
     int64_t n_zero_rows;
+    int l2_hints;             // bit 0: keep X in L2 (evict_last); bit 1: stream A and Y (evict_first)
 };
 
 struct TupleView {
@@ -81,26 +82,37 @@ __device__ __forceinline__ void fma4(float4 &acc, float a, const float4 &v)
     acc.w = fmaf(a, v.w, acc.w);
 }
 
+// UNROLL independent 16-byte loads are in flight per lane before the first FMA needs one.
+template <int UNROLL>
 __device__ __forceinline__ float4 gather_vec4(const int2 *pairs, int count, int first, int step,
-                                              const float *__restrict__ x, int64_t ldx, bool active)
+                                              const float *__restrict__ x, int64_t ldx, bool active, uint64_t keep)
 {
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     if (!active) return acc;
     int i = first;
-    for (; i + 3 * step < count; i += 4 * step) {
-        const int2 p0 = pairs[i], p1 = pairs[i + step], p2 = pairs[i + 2 * step], p3 = pairs[i + 3 * step];
-        const float4 v0 = ld_x4(x + (int64_t)p0.x * ldx);
-        const float4 v1 = ld_x4(x + (int64_t)p1.x * ldx);
-        const float4 v2 = ld_x4(x + (int64_t)p2.x * ldx);
-        const float4 v3 = ld_x4(x + (int64_t)p3.x * ldx);
-        fma4(acc, __int_as_float(p0.y), v0);
-        fma4(acc, __int_as_float(p1.y), v1);
-        fma4(acc, __int_as_float(p2.y), v2);
-        fma4(acc, __int_as_float(p3.y), v3);
+    for (; i + (UNROLL - 1) * step < count; i += UNROLL * step) {
+        int2 p[UNROLL];
+        float4 v[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; u++) p[u] = pairs[i + u * step];
+#pragma unroll
+        for (int u = 0; u < UNROLL; u++) v[u] = ld_x4(x + (int64_t)p[u].x * ldx, keep);
+#pragma unroll
+        for (int u = 0; u < UNROLL; u++) fma4(acc, __int_as_float(p[u].y), v[u]);
     }
-    for (; i < count; i += step) {
-        const int2 p0 = pairs[i];
-        fma4(acc, __int_as_float(p0.y), ld_x4(x + (int64_t)p0.x * ldx));
+    if (i < count) {
+        // tail: the same batch with the loads past the end switched off
+        int2 p[UNROLL - 1];
+        float4 v[UNROLL - 1];
+#pragma unroll
+        for (int u = 0; u < UNROLL - 1; u++) {
+            const bool live = i + u * step < count;
+            p[u] = live ? pairs[i + u * step] : make_int2(0, 0);
+            v[u] = live ? ld_x4(x + (int64_t)p[u].x * ldx, keep) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL - 1; u++)
+            if (i + u * step < count) fma4(acc, __int_as_float(p[u].y), v[u]);
     }
     return acc;
 }
@@ -108,7 +120,7 @@ __device__ __forceinline__ float4 gather_vec4(const int2 *pairs, int count, int 
 constexpr int SPMM_SCALAR_COLS = SPMM_PANEL / 32;   // columns per lane in scalar mode
 
 __device__ __forceinline__ void gather_scalar(const int2 *pairs, int count, const float *__restrict__ x,
-                                              int64_t ldx, int dim, float (&acc)[SPMM_SCALAR_COLS])
+                                              int64_t ldx, int dim, float (&acc)[SPMM_SCALAR_COLS], uint64_t keep)
 {
     const int lane = lane_id();
 #pragma unroll
@@ -120,7 +132,7 @@ __device__ __forceinline__ void gather_scalar(const int2 *pairs, int count, cons
 #pragma unroll
         for (int k = 0; k < SPMM_SCALAR_COLS; k++) {
             const int c = lane + 32 * k;
-            if (c < dim) acc[k] = fmaf(a, ld_x1(xr + c), acc[k]);
+            if (c < dim) acc[k] = fmaf(a, ld_x1(xr + c, keep), acc[k]);
         }
     }
 }
@@ -130,7 +142,7 @@ __device__ __forceinline__ void gather_scalar(const int2 *pairs, int count, cons
 // dim % 4 == 0, dim <= 4*S and 16-byte aligned rows); S = 0 is the scalar
 // mode for every other dim (lane l owns columns l, l+32, l+64, l+96).
 // ---------------------------------------------------------------------------
-template <int S>
+template <int S, int UNROLL>
 __global__ void __launch_bounds__(SPMM_THREADS)
 spmm_units_kernel(const SpmmParams p)
 {
@@ -146,6 +158,9 @@ spmm_units_kernel(const SpmmParams p)
     const int slot = lane / LANES, sl = lane % LANES;
     const int col = VEC ? sl * 4 : sl;
     const bool active = col < p.dim;
+    L2Policies pol = make_l2_policies();
+    if (!(p.l2_hints & 1)) pol.keep = (p.l2_hints & 4) ? 0 : make_l2_policy_normal();
+    if (!(p.l2_hints & 2)) pol.stream = (p.l2_hints & 4) ? 0 : make_l2_policy_normal();
 
     if ((int64_t)blockIdx.x >= p.n_units) {
         // zero-fill rows that no tuple covers
@@ -154,9 +169,9 @@ spmm_units_kernel(const SpmmParams p)
             if (zb + k >= p.n_zero_rows) break;
             float *yr = p.y + (int64_t)p.zero_rows[zb + k] * p.ldy;
             if (VEC) {
-                if (active) st_y4(yr + col, make_float4(0.f, 0.f, 0.f, 0.f));
+                if (active) st_y4(yr + col, make_float4(0.f, 0.f, 0.f, 0.f), pol.stream);
             } else {
-                for (int c = lane; c < p.dim; c += 32) yr[c] = 0.f;
+                for (int c = lane; c < p.dim; c += 32) st_y1(yr + c, 0.f, pol.stream);
             }
         }
         return;
@@ -171,7 +186,8 @@ spmm_units_kernel(const SpmmParams p)
         const int *__restrict__ gi = p.idx + t.loc;
         const float *__restrict__ gv = p.val + t.loc;
 #pragma unroll 4
-        for (int k = lane; k < total; k += 32) s_pair[w][k] = make_int2(ld_a(gi + k), __float_as_int(ld_a(gv + k)));
+        for (int k = lane; k < total; k += 32)
+            s_pair[w][k] = make_int2(ld_a(gi + k, pol.stream), __float_as_int(ld_a(gv + k, pol.stream)));
     }
     __syncwarp();
 
@@ -183,13 +199,13 @@ spmm_units_kernel(const SpmmParams p)
         if (t.small && NS > 1 && t.row_nz <= 32) {
             // one slot per row
             for (int r = slot; r < t.n_rows; r += NS) {
-                const float4 acc = gather_vec4(pairs + r * t.row_nz, t.row_nz, 0, 1, xc, p.ldx, active);
-                if (active) st_y4(p.y + (int64_t)(t.row0 + r) * p.ldy + col, acc);
+                const float4 acc = gather_vec4<UNROLL>(pairs + r * t.row_nz, t.row_nz, 0, 1, xc, p.ldx, active, pol.keep);
+                if (active) st_y4(p.y + (int64_t)(t.row0 + r) * p.ldy + col, acc, pol.stream);
             }
         } else {
             // the slots of the warp share each row
             for (int r = 0; r < t.n_rows; r++) {
-                float4 acc = gather_vec4(pairs + r * t.row_nz, t.row_nz, slot, NS, xc, p.ldx, active);
+                float4 acc = gather_vec4<UNROLL>(pairs + r * t.row_nz, t.row_nz, slot, NS, xc, p.ldx, active, pol.keep);
 #pragma unroll
                 for (int off = LANES; off < 32; off <<= 1) {
                     acc.x += __shfl_xor_sync(FULL_MASK, acc.x, off);
@@ -198,7 +214,7 @@ spmm_units_kernel(const SpmmParams p)
                     acc.w += __shfl_xor_sync(FULL_MASK, acc.w, off);
                 }
                 if (slot == 0 && active) {
-                    if (t.small) st_y4(p.y + (int64_t)(t.row0 + r) * p.ldy + col, acc);
+                    if (t.small) st_y4(p.y + (int64_t)(t.row0 + r) * p.ldy + col, acc, pol.stream);
                     else *reinterpret_cast<float4 *>(&s_part[w][col]) = acc;
                 }
             }
@@ -206,12 +222,12 @@ spmm_units_kernel(const SpmmParams p)
     } else {
         for (int r = 0; r < t.n_rows; r++) {
             float acc[SPMM_SCALAR_COLS];
-            gather_scalar(pairs + r * t.row_nz, t.row_nz, p.x, p.ldx, p.dim, acc);
+            gather_scalar(pairs + r * t.row_nz, t.row_nz, p.x, p.ldx, p.dim, acc, pol.keep);
 #pragma unroll
             for (int k = 0; k < SPMM_SCALAR_COLS; k++) {
                 const int c = lane + 32 * k;
                 if (c < p.dim) {
-                    if (t.small) p.y[(int64_t)(t.row0 + r) * p.ldy + c] = acc[k];
+                    if (t.small) st_y1(p.y + (int64_t)(t.row0 + r) * p.ldy + c, acc[k], pol.stream);
                     else s_part[w][c] = acc[k];
                 }
             }
@@ -239,7 +255,7 @@ spmm_units_kernel(const SpmmParams p)
                 const float4 v = *reinterpret_cast<const float4 *>(&s_part[ww][col]);
                 sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
             }
-            st_y4(dst + col, sum);
+            *reinterpret_cast<float4 *>(dst + col) = sum;
         }
     } else {
         for (int c = lane; c < p.dim; c += 32) {
@@ -273,7 +289,7 @@ spmm_carry_kernel(const float *__restrict__ carry, const int *__restrict__ carry
                 const float4 v = *reinterpret_cast<const float4 *>(carry + q * SPMM_PANEL + col);
                 sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
             }
-            st_y4(y + (int64_t)row * ldy + col, sum);
+            *reinterpret_cast<float4 *>(y + (int64_t)row * ldy + col) = sum;
         }
     } else {
         for (int c = lane; c < dim; c += 32) {
