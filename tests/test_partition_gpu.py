@@ -92,3 +92,19 @@ def test_error_behaviour():
     out = np.zeros((2, 4), dtype=np.int32)
     assert lib.agcn_partition_host(ip.ctypes.data, 3, out.ctypes.data, 2, ctypes.byref(n)) == _lib.ERR_CAPACITY
     assert n.value == 4                                                           # 1 + ceil(998 / 384)
+
+
+def test_drop_in_script_same_files_as_the_reference(kat, tmp_path):
+    # run like the reference script: cwd holding ./graphs/<g>.config + .new_indptr -> ./block_level_meta/<g>.block4
+    import subprocess, sys, os
+    from conftest import PKG
+    require_cuda()
+    os.makedirs(tmp_path / "graphs")
+    for name in ("pubmed", "collab"):
+        (tmp_path / "graphs" / f"{name}.config").write_text("")
+        kat_indptr(kat[name]).tofile(tmp_path / "graphs" / f"{name}.new_indptr")
+    subprocess.check_call([sys.executable, os.path.join(PKG, "block_level_partition.py")], cwd=tmp_path,
+                          stdout=subprocess.DEVNULL)
+    for name in ("pubmed", "collab"):
+        got = np.fromfile(tmp_path / "block_level_meta" / f"{name}.block4", dtype=np.int32)
+        assert sha256_block4(got) == kat[name]["sha256"], name
