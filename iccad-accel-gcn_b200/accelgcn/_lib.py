@@ -14,6 +14,7 @@ DEFAULT_LIB = os.path.join(os.path.dirname(_HERE), "lib", "libaccelgcn.so")
 
 OK, ERR_INVALID, ERR_CUDA, ERR_CAPACITY, ERR_RANGE = 0, -1, -2, -3, -4
 DEG_BOUND = 384
+PARTITION_NOALLOC_MAX_ROWS = 1 << 24
 
 _vp, _i64, _int = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int
 
@@ -23,6 +24,7 @@ PROTOTYPES = {
     "agcn_version": (_int, []),
     "agcn_partition_device": (_int, [_vp, _i64, _vp, _i64, ctypes.POINTER(_i64), _vp]),
     "agcn_partition_host": (_int, [_vp, _i64, _vp, _i64, ctypes.POINTER(_i64)]),
+    "agcn_partition_device_noalloc": (_int, [_vp, _i64, _vp, _i64, ctypes.POINTER(_i64), _vp]),
     "agcn_degree_sort_device": (_int, [_vp, _vp, _vp, _i64, _i64, _int, _vp, _vp, _vp, _vp, _vp]),
     "agcn_degree_sort_host": (_int, [_vp, _vp, _vp, _i64, _i64, _int, _vp, _vp, _vp, _vp]),
     "agcn_spmm_create": (_int, [ctypes.POINTER(_vp), _vp, _i64, _vp, _i64, _i64, _i64, _vp]),

@@ -67,6 +67,25 @@ int agcn_partition_device(const int32_t *d_indptr, int64_t n_rows,
 int agcn_partition_host(const int32_t *h_indptr, int64_t n_rows,
                         int32_t *h_block4, int64_t cap_blocks, int64_t *n_blocks);
 
+/* Partitioner that allocates nothing.  It has no counterpart in the
+ * reference; it exists for hosts that cannot let a library call cudaMalloc --
+ * processes whose own allocator already owns all device memory, loops that
+ * cannot take the device-wide synchronisation an allocation or free implies,
+ * plug-in hosts that forbid allocation after start-up.  Same arguments, same
+ * results and same error codes as agcn_partition_device, but the tile scratch
+ * is a fixed array inside the library's device image (about 96 KB, resident on
+ * every GPU that loads the library until the process exits) and the call makes
+ * no cudaMalloc / cudaFree or other allocating call.
+ *  - n_rows above AGCN_PARTITION_NOALLOC_MAX_ROWS is AGCN_ERR_INVALID.
+ *  - The first call on each device looks up the array's device address; make
+ *    that first call before any stream capture begins.
+ *  - All calls on a GPU share the array: calls that overlap on the same GPU
+ *    (other streams or threads) race and must be serialised by the caller. */
+#define AGCN_PARTITION_NOALLOC_MAX_ROWS 16777216   /* 2^24 */
+int agcn_partition_device_noalloc(const int32_t *d_indptr, int64_t n_rows,
+                                  int32_t *d_block4, int64_t cap_blocks, int64_t *n_blocks,
+                                  void *stream);
+
 /* ------------------------------------------------------------------------
  * Degree sort.
  * Produces the degree-ordered CSR the reference only assumes -- its inputs
