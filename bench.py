@@ -308,21 +308,33 @@ def ours(args, rank, world, local_rank):
         del full
     e2e_steps = max(1, min(args.steps, 5))
 
-    def e2e_step():
-        for d in dims:
-            host(hb["b4"], hb["ix"], hb["v"], hx[d], r1 - r0, out=hy[d])
+    n_cols_host = int(hx[dims[0]].shape[0])
 
-    e2e_step()
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        e2e_step()
-    barrier()
-    e2e_s = torch.tensor([time.perf_counter() - t0], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(e2e_s, op=dist.ReduceOp.MAX)
-    e2e_value = flops_step * e2e_steps / float(e2e_s.item()) / 1e9
-    h2d = sum(16 * n_blocks_local + 8 * int(shard.indices.numel()) + 4 * d * int(hx[d].shape[0]) for d in dims)
+    def e2e_step(with_graph=True):
+        # every input of the step crosses PCIe once: the graph (.block4, column ids, values), then
+        # per width X up and Y down
+        if with_graph:
+            host.set_graph(hb["b4"], hb["ix"], hb["v"], r1 - r0, n_cols_host)
+        for d in dims:
+            host.run(hx[d], out=hy[d])
+
+    def timed(fn, reps):
+        fn()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            fn()
+        barrier()
+        dt = torch.tensor([time.perf_counter() - t0], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+        return float(dt.item())
+
+    e2e_s = timed(e2e_step, e2e_steps)
+    e2e_value = flops_step * e2e_steps / e2e_s / 1e9
+    resident_s = timed(lambda: e2e_step(False), e2e_steps)           # graph uploaded once, at set-up
+    graph_bytes = 16 * n_blocks_local + 8 * int(shard.indices.numel())
+    h2d = graph_bytes + sum(4 * d * n_cols_host for d in dims)
     d2h = sum(4 * d * (r1 - r0) for d in dims)
     e2e_ok = bool(torch.equal(hy[dims[-1]], ys[dims[-1]].cpu()))     # same bits as the resident run
     host.close()
@@ -353,7 +365,12 @@ def ours(args, rank, world, local_rank):
             "config": workload_description(args.workload, g.info, n, nnz, n_blocks, dims),
             "roofline": roofline, "per_dim": per_dim, "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "steps": e2e_steps, "bit_identical_to_resident_run": e2e_ok},
+                    "steps": e2e_steps, "ms_per_step": e2e_s / e2e_steps * 1e3,
+                    "pcie_gbs": (h2d + d2h) / (e2e_s / e2e_steps) / 1e9,
+                    "bit_identical_to_resident_run": e2e_ok,
+                    "graph_resident": {"value": flops_step * e2e_steps / resident_s / 1e9, "unit": UNIT,
+                                       "h2d_bytes_per_step": h2d - graph_bytes, "d2h_bytes_per_step": d2h,
+                                       "note": "graph uploaded once at set-up (SPMM_BASE constructor), X and Y cross PCIe every step"}},
             "gpu_launches": launches_per_step * args.steps,
             "plan": shard.plan.info()}
 

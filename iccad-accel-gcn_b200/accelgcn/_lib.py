@@ -34,6 +34,8 @@ PROTOTYPES = {
                                   ctypes.POINTER(_int)]),
     "agcn_host_ctx_create": (_int, [ctypes.POINTER(_vp)]),
     "agcn_host_ctx_destroy": (_int, [_vp]),
+    "agcn_host_set_graph": (_int, [_vp, _vp, _i64, _vp, _vp, _i64, _i64, _i64]),
+    "agcn_host_spmm": (_int, [_vp, _vp, _vp, _int]),
     "agcn_spmm_host": (_int, [_vp, _vp, _i64, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int]),
 }
 

@@ -144,6 +144,21 @@ class HostSpmm:
         _lib.check(self._lib.agcn_host_ctx_create(ctypes.byref(h)))
         self._h = h
 
+    def set_graph(self, block4, indices, vals, n_rows: int, n_cols: int) -> None:
+        """Upload .block4, column ids and values and build the plan (the constructor's share of the plug-in)."""
+        self._n_rows, self._n_cols = int(n_rows), int(n_cols)
+        _lib.check(self._lib.agcn_host_set_graph(self._h, _addr(block4), _numel(block4) // 4, _addr(indices),
+                                                 _addr(vals), n_rows, n_cols, _numel(indices)))
+
+    def run(self, x, out=None):
+        """One product on host operands: X up, SpMM, Y down."""
+        dim = x.shape[1]
+        if x.shape[0] != self._n_cols:
+            raise ValueError("X has the wrong number of rows")
+        y = out if out is not None else np.empty((self._n_rows, dim), dtype=np.float32)
+        _lib.check(self._lib.agcn_host_spmm(self._h, _addr(x), _addr(y), dim))
+        return y
+
     def __call__(self, block4, indices, vals, x, n_rows: int, out=None):
         n_cols, dim = x.shape
         y = out if out is not None else np.empty((n_rows, dim), dtype=np.float32)

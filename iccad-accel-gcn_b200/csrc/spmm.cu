@@ -225,12 +225,14 @@ extern "C" int agcn_spmm_plan_info(const agcn_spmm_plan *plan, int64_t *n_units,
 }
 
 // ---------------------------------------------------------------------------
-// host-buffer call
+// host-buffer calls
 // ---------------------------------------------------------------------------
 struct agcn_host_ctx {
     cudaStream_t stream = nullptr;
     void *buf[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};   // block4, idx, val, x, y
     size_t cap[5] = {0, 0, 0, 0, 0};
+    agcn_spmm_plan *plan = nullptr;          // of the graph set by agcn_host_set_graph
+    int64_t n_rows = 0, n_cols = 0, nnz = 0;
 };
 
 namespace agcn {
@@ -241,6 +243,48 @@ static int ctx_reserve(agcn_host_ctx *c, int which, size_t bytes)
     c->buf[which] = nullptr; c->cap[which] = 0;
     AGCN_CUDA(cudaMalloc(&c->buf[which], bytes));
     c->cap[which] = bytes;
+    return AGCN_OK;
+}
+
+static int host_set_graph(agcn_host_ctx *ctx, const int *h_block4, int64_t n_blocks, const int *h_indices,
+                          const float *h_vals, int64_t n_rows, int64_t n_cols, int64_t nnz)
+{
+    AGCN_REQUIRE(ctx != nullptr, "agcn_host_set_graph: null context");
+    AGCN_REQUIRE(n_blocks >= 0 && (n_blocks == 0 || h_block4 != nullptr), "agcn_host_set_graph: null block4");
+    AGCN_REQUIRE(nnz >= 0 && (nnz == 0 || (h_indices != nullptr && h_vals != nullptr)), "agcn_host_set_graph: null indices or values");
+    AGCN_REQUIRE(n_rows > 0 && n_cols > 0, "agcn_host_set_graph: bad sizes");
+    plan_free(ctx->plan);
+    ctx->plan = nullptr;
+    const size_t bytes[3] = {(size_t)n_blocks * 16, (size_t)nnz * 4, (size_t)nnz * 4};
+    const void *src[3] = {h_block4, h_indices, h_vals};
+    for (int i = 0; i < 3; i++) {
+        int rc = ctx_reserve(ctx, i, bytes[i] > 0 ? bytes[i] : 16);
+        if (rc != AGCN_OK) return rc;
+        if (bytes[i] > 0) AGCN_CUDA(cudaMemcpyAsync(ctx->buf[i], src[i], bytes[i], cudaMemcpyHostToDevice, ctx->stream));
+    }
+    ctx->n_rows = n_rows; ctx->n_cols = n_cols; ctx->nnz = nnz;
+    return spmm_create(&ctx->plan, static_cast<const int *>(ctx->buf[0]), n_blocks, static_cast<const int *>(ctx->buf[1]),
+                       n_rows, n_cols, nnz, ctx->stream);
+}
+
+static int host_spmm(agcn_host_ctx *ctx, const float *h_x, float *h_y, int dim)
+{
+    AGCN_REQUIRE(ctx != nullptr && ctx->plan != nullptr, "agcn_host_spmm: no graph set (call agcn_host_set_graph first)");
+    AGCN_REQUIRE(h_x != nullptr && h_y != nullptr && dim >= 1, "agcn_host_spmm: null X or Y, or dim < 1");
+    const size_t xb = (size_t)ctx->n_cols * dim * 4, yb = (size_t)ctx->n_rows * dim * 4;
+    int rc = ctx_reserve(ctx, 3, xb);
+    if (rc == AGCN_OK) rc = ctx_reserve(ctx, 4, yb);
+    if (rc != AGCN_OK) return rc;
+    cudaStream_t s = ctx->stream;
+    AGCN_CUDA(cudaMemcpyAsync(ctx->buf[3], h_x, xb, cudaMemcpyHostToDevice, s));
+    rc = spmm_run(ctx->plan, static_cast<const int *>(ctx->buf[1]), static_cast<const float *>(ctx->buf[2]),
+                  static_cast<const float *>(ctx->buf[3]), dim, static_cast<float *>(ctx->buf[4]), dim, dim, s);
+    if (rc != AGCN_OK) {
+        cudaStreamSynchronize(s);
+        return rc;
+    }
+    AGCN_CUDA(cudaMemcpyAsync(h_y, ctx->buf[4], yb, cudaMemcpyDeviceToHost, s));
+    AGCN_CUDA(cudaStreamSynchronize(s));
     return AGCN_OK;
 }
 }  // namespace agcn
@@ -267,49 +311,33 @@ extern "C" int agcn_host_ctx_destroy(agcn_host_ctx *ctx)
 {
     agcn::clear_error();
     if (ctx == nullptr) return AGCN_OK;
+    agcn::plan_free(ctx->plan);
     for (int i = 0; i < 5; i++) cudaFree(ctx->buf[i]);
     if (ctx->stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
     return AGCN_OK;
 }
 
+extern "C" int agcn_host_set_graph(agcn_host_ctx *ctx, const int32_t *h_block4, int64_t n_blocks,
+                                   const int32_t *h_indices, const float *h_vals,
+                                   int64_t n_rows, int64_t n_cols, int64_t nnz)
+{
+    agcn::clear_error();
+    return agcn::host_set_graph(ctx, h_block4, n_blocks, h_indices, h_vals, n_rows, n_cols, nnz);
+}
+
+extern "C" int agcn_host_spmm(agcn_host_ctx *ctx, const float *h_x, float *h_y, int dim)
+{
+    agcn::clear_error();
+    return agcn::host_spmm(ctx, h_x, h_y, dim);
+}
+
 extern "C" int agcn_spmm_host(agcn_host_ctx *ctx, const int32_t *h_block4, int64_t n_blocks,
                               const int32_t *h_indices, const float *h_vals, const float *h_x, float *h_y,
                               int64_t n_rows, int64_t n_cols, int64_t nnz, int dim)
 {
-    using namespace agcn;
-    clear_error();
-    AGCN_REQUIRE(ctx != nullptr, "agcn_spmm_host: null context");
-    AGCN_REQUIRE(h_x != nullptr && h_y != nullptr, "agcn_spmm_host: null X or Y");
-    AGCN_REQUIRE(n_blocks >= 0 && (n_blocks == 0 || h_block4 != nullptr), "agcn_spmm_host: null block4");
-    AGCN_REQUIRE(nnz >= 0 && (nnz == 0 || (h_indices != nullptr && h_vals != nullptr)), "agcn_spmm_host: null indices or values");
-    AGCN_REQUIRE(n_rows > 0 && n_cols > 0 && dim >= 1, "agcn_spmm_host: bad sizes");
-    const size_t bytes[5] = {(size_t)n_blocks * 16, (size_t)nnz * 4, (size_t)nnz * 4,
-                             (size_t)n_cols * dim * 4, (size_t)n_rows * dim * 4};
-    for (int i = 0; i < 5; i++) {
-        int rc = ctx_reserve(ctx, i, bytes[i] > 0 ? bytes[i] : 16);
-        if (rc != AGCN_OK) return rc;
-    }
-    cudaStream_t s = ctx->stream;
-    const void *src[4] = {h_block4, h_indices, h_vals, h_x};
-    for (int i = 0; i < 4; i++)
-        if (bytes[i] > 0) AGCN_CUDA(cudaMemcpyAsync(ctx->buf[i], src[i], bytes[i], cudaMemcpyHostToDevice, s));
-    agcn_spmm_plan *plan = nullptr;
-    int rc = spmm_create(&plan, static_cast<const int *>(ctx->buf[0]), n_blocks, static_cast<const int *>(ctx->buf[1]),
-                         n_rows, n_cols, nnz, s);
+    agcn::clear_error();
+    int rc = agcn::host_set_graph(ctx, h_block4, n_blocks, h_indices, h_vals, n_rows, n_cols, nnz);
     if (rc != AGCN_OK) return rc;
-    rc = spmm_run(plan, static_cast<const int *>(ctx->buf[1]), static_cast<const float *>(ctx->buf[2]),
-                  static_cast<const float *>(ctx->buf[3]), dim, static_cast<float *>(ctx->buf[4]), dim, dim, s);
-    if (rc == AGCN_OK) {
-        cudaError_t e = cudaMemcpyAsync(h_y, ctx->buf[4], bytes[4], cudaMemcpyDeviceToHost, s);
-        if (e == cudaSuccess) e = cudaStreamSynchronize(s);
-        if (e != cudaSuccess) {
-            set_error("agcn_spmm_host: download of Y: %s", cudaGetErrorString(e));
-            rc = AGCN_ERR_CUDA;
-        }
-    } else {
-        cudaStreamSynchronize(s);
-    }
-    plan_free(plan);
-    return rc;
+    return agcn::host_spmm(ctx, h_x, h_y, dim);
 }

@@ -150,16 +150,27 @@ int agcn_spmm_plan_info(const agcn_spmm_plan *plan, int64_t *n_units, int64_t *n
                         int64_t *n_zero_rows, int *launches_last_run);
 
 /* ------------------------------------------------------------------------
- * Host-buffer SpMM: the whole plugin call with host arrays, as a harness
- * that keeps its data in host memory would issue it -- upload .block4,
- * indices, values and X, run, download Y.  The context keeps device buffers
- * between calls (they only grow) and owns one stream.  Host pointers may be
- * pageable or pinned; pinned memory gives full PCIe speed.
+ * Host-buffer SpMM: the plug-in used by a harness that keeps its arrays in
+ * host memory.  The split follows SPMM_BASE: agcn_host_set_graph is the
+ * constructor's part (spmm_base.h:9-20 takes ptr/idx/val once) plus the
+ * .block4 load of do_test (spmm_accel.cu:122) -- it uploads .block4, column
+ * ids and values and builds the plan; agcn_host_spmm is one run(dim)
+ * (spmm_accel.cu:104-108) on host operands -- it uploads X [n_cols x dim],
+ * runs, downloads Y [n_rows x dim] and returns when Y is complete.
+ * agcn_spmm_host does both in one call.  The context owns one stream and
+ * keeps its device buffers between calls (they only grow).  Host pointers may
+ * be pageable or pinned; pinned memory gives full PCIe speed.
  * ---------------------------------------------------------------------- */
 typedef struct agcn_host_ctx agcn_host_ctx;
 
 int agcn_host_ctx_create(agcn_host_ctx **ctx);
 int agcn_host_ctx_destroy(agcn_host_ctx *ctx);
+
+int agcn_host_set_graph(agcn_host_ctx *ctx, const int32_t *h_block4, int64_t n_blocks,
+                        const int32_t *h_indices, const float *h_vals,
+                        int64_t n_rows, int64_t n_cols, int64_t nnz);
+
+int agcn_host_spmm(agcn_host_ctx *ctx, const float *h_x, float *h_y, int dim);
 
 int agcn_spmm_host(agcn_host_ctx *ctx, const int32_t *h_block4, int64_t n_blocks,
                    const int32_t *h_indices, const float *h_vals,

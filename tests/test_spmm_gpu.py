@@ -160,7 +160,17 @@ def test_host_buffer_entry_point(cfg1):
         x = cfg1.x(dim)
         y = h(cfg1.block4, cfg1.idx, cfg1.val, x, cfg1.n)
         cfg1.check(x, y)
+    # constructor / run split of the plug-in: the graph goes up once, every run moves X and Y only
+    h.set_graph(cfg1.block4, cfg1.idx, cfg1.val, cfg1.n, cfg1.n)
+    for dim in (16, 100):
+        x = cfg1.x(dim)
+        cfg1.check(x, h.run(x))
     h.close()
+    h2 = spmm.HostSpmm()
+    with pytest.raises(spmm._lib.AccelGcnError, match="no graph set"):
+        h2._n_rows, h2._n_cols = cfg1.n, cfg1.n
+        h2.run(cfg1.x(16))
+    h2.close()
 
 
 def test_plugin_class_mirrors_reference_do_test(cfg1, tmp_path):
