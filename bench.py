@@ -44,6 +44,7 @@ WORKLOADS = {
 }
 METRIC, UNIT = "spmm_gflops", "GFLOP/s"
 FALLBACK_HBM_GBS = 6650.0
+NCU_TRAFFIC_BYTES = {("cfg2", 128): 3.781e9}      # (workload, dim) -> DRAM bytes per product, from ncu
 
 
 def hbm_peak():
@@ -144,6 +145,7 @@ def cpu_spmm_rate(ip_h, ix_h, v_h, xs, budget_s):
     """Times the CPU restatement (oracle, fp32, all OpenMP threads) on a strided row sample sized to
     take about budget_s seconds over all widths.  Returns (GFLOP/s, seconds, sample description, stride)."""
     from oracle import oracle
+    oracle.use_all_host_threads()
     n, nnz = len(ip_h) - 1, len(ix_h)
     dsum = sum(x.shape[1] for x in xs)
     probe_stride = max(1, n // 2048)
@@ -354,8 +356,11 @@ def ours(args, rank, world, local_rank):
                         "gather_gbs_l2_inclusive": (nnz * (8 + 4 * d) + 4 * d * n + 16 * n_blocks) / ms / 1e6})
     top = max(per_dim, key=lambda r: r["ms"])
     fp32_peak = props.multi_processor_count * 128 * 2 * (clocks["sm_mhz"] or clocks["sm_max_mhz"] or 1965.0) * 1e6
+    # dram__bytes_read + dram__bytes_write of that product from the ncu capture summarised in
+    # profiles/spmm_units_kernel_cfg2.md (known for the default workload on one GPU only)
+    traffic = NCU_TRAFFIC_BYTES.get((args.workload, top["dim"])) if world == 1 else None
     roofline = {"bound": "hbm", "achieved": top["hbm_gbs"], "peak": peak, "unit": "GB/s",
-                "frac": top["hbm_frac"], "traffic": None, "kernel": f"spmm_units_kernel dim={top['dim']}",
+                "frac": top["hbm_frac"], "traffic": traffic, "kernel": f"spmm_units_kernel dim={top['dim']}",
                 "peak_source": peak_src,
                 "algorithmic_bytes_per_launch": min_bytes(nnz, n_blocks, n, n, top["dim"]),
                 "fp32_frac_at_sampled_clock": 2.0 * nnz * top["dim"] / (top["ms"] / 1e3) / fp32_peak}

@@ -105,10 +105,13 @@ class ShardedSpmm:
     def row_range(self):
         return int(self.cuts[self.rank]), int(self.cuts[self.rank + 1])
 
-    def step(self, x_local, y_local):
-        """y_local[n_local x dim] = A_shard @ allgather(x_local).  Asynchronous on the current stream."""
-        dim = x_local.shape[1]
-        if self.world == 1:
+    def step(self, x_local, y_local, x_gathered=None):
+        """y_local[n_local x dim] = A_shard @ allgather(x_local).  Asynchronous on the current stream.
+        x_gathered, if given, is an already gathered padded operand (the collective is skipped)."""
+        dim = y_local.shape[1]
+        if x_gathered is not None:
+            x_full = x_gathered
+        elif self.world == 1:
             x_full = x_local
         else:
             buf = self._gather.get(dim)

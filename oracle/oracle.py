@@ -202,6 +202,16 @@ def num_threads() -> int:
     return int(_lib().agcn_oracle_num_threads())
 
 
+def use_all_host_threads() -> int:
+    """Let the OpenMP loops use every core this process may run on, whatever OMP_NUM_THREADS says."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    _lib().agcn_oracle_set_num_threads(n)
+    return num_threads()
+
+
 # --------------------------------------------------------------------------
 # The reference's own CUDA kernels, compiled from its sources into
 # oracle/_ref/libref_accel.so by `make -C oracle ref` (needs the reference

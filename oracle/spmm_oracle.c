@@ -124,6 +124,16 @@ int agcn_oracle_spmm_csr_f32(const int32_t *indptr, const int32_t *idx, const fl
     return 0;
 }
 
+/* Use n OpenMP threads from now on (launchers such as torchrun export OMP_NUM_THREADS=1). */
+void agcn_oracle_set_num_threads(int n)
+{
+#ifdef _OPENMP
+    if (n >= 1) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int agcn_oracle_num_threads(void)
 {
 #ifdef _OPENMP

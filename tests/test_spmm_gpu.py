@@ -232,3 +232,31 @@ def test_parity_with_the_reference_kernel_heavy_rows(cfg4_small):
     assert spmm_close(y, ref, row_abs_scale(cfg4_small.indptr, cfg4_small.val, x)).all()
     cs = oracle.ref_cusparse_spmm(cfg4_small.indptr, cfg4_small.idx, cfg4_small.val, x)
     assert spmm_close(y, cs, row_abs_scale(cfg4_small.indptr, cfg4_small.val, x)).all()
+
+
+@pytest.mark.parametrize("world", [2, 5])
+def test_row_sharded_product_on_one_gpu_equals_unsharded(cfg4_small, world):
+    # every rank's shard built and multiplied in this one process (the all-gather is replaced by
+    # assembling the padded operand by hand): shard-local .block4, renumbered columns, padded X
+    import torch
+    from accelgcn import sharded
+    c = cfg4_small
+    dev = c.dev
+    ip, ix, v = (torch.from_numpy(a).to(dev) for a in (c.indptr, c.idx, c.val))
+    x = c.x(64)
+    parts = []
+    for r in range(world):
+        sh = sharded.ShardedSpmm(ip, ix, v, r, world)
+        xg = torch.zeros((world * sh.max_rows, 64), dtype=torch.float32, device=dev)
+        for q in range(world):
+            q0, q1 = int(sh.cuts[q]), int(sh.cuts[q + 1])
+            xg[q * sh.max_rows: q * sh.max_rows + (q1 - q0)] = torch.from_numpy(x[q0:q1]).to(dev)
+        y = torch.full((sh.n_local, 64), float("nan"), dtype=torch.float32, device=dev)
+        sh.step(None, y, x_gathered=xg)
+        torch.cuda.synchronize()
+        parts.append(y.cpu().numpy())
+        sh.close()
+    y = np.concatenate(parts)
+    c.check(x, y)
+    nnz_per_rank = np.diff(c.indptr[sharded.nnz_balanced_cuts(c.indptr, world)].astype(np.int64))
+    assert nnz_per_rank.max() - nnz_per_rank.min() <= 2 * np.diff(c.indptr).max()
