@@ -23,6 +23,23 @@ def _inputs():
     return files
 
 
+HARNESS = os.path.join(HERE, "lib", "spmm_test")
+HARNESS_SOURCES = ["spmm_test.cu", "spmm_accel_b200.cu"]
+
+
+def build_harness(force: bool = False) -> str:
+    """lib/spmm_test: the reference-compatible benchmark harness (cpp/), linked against the library."""
+    build()
+    srcs = [os.path.join(HERE, "cpp", s) for s in HARNESS_SOURCES]
+    deps = srcs + [os.path.join(HERE, "cpp", h) for h in ("spmm_plugin.h", "spmm_accel_b200.h")] + [LIB]
+    if not force and os.path.exists(HARNESS) and all(os.path.getmtime(f) <= os.path.getmtime(HARNESS) for f in deps):
+        return HARNESS
+    cmd = ["nvcc", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-o", HARNESS, *srcs,
+           "-L" + os.path.dirname(LIB), "-laccelgcn", "-lcusparse", "-Xlinker", "-rpath=$ORIGIN"]
+    subprocess.check_call(cmd)
+    return HARNESS
+
+
 def build(force: bool = False, verbose: bool = False) -> str:
     if not force and os.path.exists(LIB) and all(os.path.getmtime(f) <= os.path.getmtime(LIB) for f in _inputs()):
         return LIB
@@ -35,3 +52,4 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build_harness(force="--force" in sys.argv))

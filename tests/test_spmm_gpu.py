@@ -260,3 +260,22 @@ def test_row_sharded_product_on_one_gpu_equals_unsharded(cfg4_small, world):
     c.check(x, y)
     nnz_per_rank = np.diff(c.indptr[sharded.nnz_balanced_cuts(c.indptr, world)].astype(np.int64))
     assert nnz_per_rank.max() - nnz_per_rank.min() <= 2 * np.diff(c.indptr).max()
+
+
+def test_cpp_harness_same_cli_and_output_as_the_reference(cfg1, tmp_path):
+    # spmm_test <graph> <dim>, run from a build directory beside graphs/ and block_level_meta/
+    # (README.md:70-73): checks against cuSPARSE, then prints the reference's timing lines
+    import subprocess, importlib.util
+    from conftest import PKG
+    from accelgcn import graphio
+    spec = importlib.util.spec_from_file_location("agcn_build", os.path.join(PKG, "build.py"))
+    mod = importlib.util.module_from_spec(spec); spec.loader.exec_module(mod)
+    exe = mod.build_harness()
+    graphio.write_graph(str(tmp_path / "graphs"), "synth1", cfg1.indptr, cfg1.idx)
+    os.makedirs(tmp_path / "block_level_meta"); os.makedirs(tmp_path / "build")
+    graphio.write_block4(str(tmp_path / "block_level_meta" / "synth1.block4"), cfg1.block4)
+    out = subprocess.run([exe, "synth1", "60"], cwd=tmp_path / "build", capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stdout + out.stderr
+    assert "validation pass!" in out.stdout and "validation fail!" not in out.stdout
+    lines = [l.split() for l in out.stdout.splitlines() if l.startswith("0/0 synth1 60 ")]
+    assert [l[3] for l in lines] == ["cusparse", "accel", "accel_event"] and all(float(l[4]) > 0 for l in lines)
