@@ -29,7 +29,9 @@ PROTOTYPES = {
     "agcn_degree_sort_host": (_int, [_vp, _vp, _vp, _i64, _i64, _int, _vp, _vp, _vp, _vp]),
     "agcn_spmm_create": (_int, [ctypes.POINTER(_vp), _vp, _i64, _vp, _i64, _i64, _i64, _vp]),
     "agcn_spmm_run": (_int, [_vp, _vp, _vp, _vp, _i64, _vp, _i64, _int, _vp]),
+    "agcn_spmm_run_act": (_int, [_vp, _vp, _vp, _vp, _i64, _vp, _i64, _int, _int, _vp]),
     "agcn_spmm_destroy": (_int, [_vp]),
+    "agcn_gemm_tf32": (_int, [_vp, _i64, _vp, _vp, _i64, _i64, _int, _int, _vp]),
     "agcn_spmm_plan_info": (_int, [_vp, ctypes.POINTER(_i64), ctypes.POINTER(_i64), ctypes.POINTER(_i64),
                                   ctypes.POINTER(_int)]),
     "agcn_host_ctx_create": (_int, [ctypes.POINTER(_vp)]),

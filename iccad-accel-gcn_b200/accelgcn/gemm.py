@@ -1,0 +1,22 @@
+"""Dense feature transform Z = H @ W of a GCN layer (agcn_gemm_tf32): fp32 in and out, TF32
+multiply on the sm_100a tensor cores.  Only 128 x 128 weights are built."""
+from __future__ import annotations
+
+from . import _lib
+
+
+def gemm_tf32(h, w, out=None, stream=None):
+    """h [m, 128] fp32 CUDA (row stride may exceed 128), w [128, 128] fp32 contiguous -> z [m, 128]."""
+    import torch
+    lib = _lib.load()
+    if not (h.is_cuda and w.is_cuda and h.dtype == torch.float32 and w.dtype == torch.float32):
+        raise TypeError("gemm_tf32 needs float32 CUDA tensors")
+    if h.dim() != 2 or w.dim() != 2 or h.shape[1] != w.shape[0] or h.stride(1) != 1 or not w.is_contiguous():
+        raise ValueError("gemm_tf32: h must be [m, k] with unit column stride, w contiguous [k, n]")
+    z = out if out is not None else torch.empty((h.shape[0], w.shape[1]), dtype=torch.float32, device=h.device)
+    s = stream if stream is not None else torch.cuda.current_stream(h.device)
+    with torch.cuda.device(h.device):
+        _lib.check(lib.agcn_gemm_tf32(h.data_ptr(), h.stride(0) if h.shape[0] > 1 else h.shape[1], w.data_ptr(),
+                                      z.data_ptr(), z.stride(0) if z.shape[0] > 1 else z.shape[1],
+                                      h.shape[0], w.shape[0], w.shape[1], s.cuda_stream))
+    return z

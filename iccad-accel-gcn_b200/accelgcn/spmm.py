@@ -39,15 +39,15 @@ class SpmmPlan:
         self._h = h
 
     def run(self, indices, vals, x, y, dim: int | None = None, ldx: int | None = None, ldy: int | None = None,
-            stream=None) -> None:
+            stream=None, relu: bool = False) -> None:
         import torch
         dim = int(x.shape[1] if dim is None else dim)
         ldx = int(x.stride(0) if ldx is None and x.dim() == 2 else (dim if ldx is None else ldx))
         ldy = int(y.stride(0) if ldy is None and y.dim() == 2 else (dim if ldy is None else ldy))
         s = stream if stream is not None else torch.cuda.current_stream(self.device)
         with torch.cuda.device(self.device):
-            _lib.check(self._lib.agcn_spmm_run(self._h, indices.data_ptr(), vals.data_ptr(), x.data_ptr(), ldx,
-                                               y.data_ptr(), ldy, dim, s.cuda_stream))
+            _lib.check(self._lib.agcn_spmm_run_act(self._h, indices.data_ptr(), vals.data_ptr(), x.data_ptr(), ldx,
+                                                   y.data_ptr(), ldy, dim, 1 if relu else 0, s.cuda_stream))
 
     def info(self) -> dict:
         a, b, c, d = ctypes.c_int64(), ctypes.c_int64(), ctypes.c_int64(), ctypes.c_int()

@@ -50,6 +50,7 @@ struct SpmmParams {
     const int *zero_rows;     // rows no tuple covers
     int64_t n_zero_rows;
     int l2_hints;             // bit 0: keep X in L2 (evict_last); bit 1: stream A and Y (evict_first)
+    int relu;                 // nonzero: Y = max(A * X, 0) (fused GCN activation)
 };
 
 struct TupleView {
@@ -74,6 +75,12 @@ __device__ __forceinline__ TupleView decode_tuple(const int4 *__restrict__ block
 // ---------------------------------------------------------------------------
 // gather-accumulate over the staged pairs  first, first+step, ... < count
 // ---------------------------------------------------------------------------
+__device__ __forceinline__ float4 relu4(const float4 &v, int on)
+{
+    return on ? make_float4(fmaxf(v.x, 0.f), fmaxf(v.y, 0.f), fmaxf(v.z, 0.f), fmaxf(v.w, 0.f)) : v;
+}
+__device__ __forceinline__ float relu1(float v, int on) { return on ? fmaxf(v, 0.f) : v; }
+
 __device__ __forceinline__ void fma4(float4 &acc, float a, const float4 &v)
 {
     acc.x = fmaf(a, v.x, acc.x);
@@ -200,7 +207,7 @@ spmm_units_kernel(const SpmmParams p)
             // one slot per row
             for (int r = slot; r < t.n_rows; r += NS) {
                 const float4 acc = gather_vec4<UNROLL>(pairs + r * t.row_nz, t.row_nz, 0, 1, xc, p.ldx, active, pol.keep);
-                if (active) st_y4(p.y + (int64_t)(t.row0 + r) * p.ldy + col, acc, pol.stream);
+                if (active) st_y4(p.y + (int64_t)(t.row0 + r) * p.ldy + col, relu4(acc, p.relu), pol.stream);
             }
         } else {
             // the slots of the warp share each row
@@ -214,7 +221,7 @@ spmm_units_kernel(const SpmmParams p)
                     acc.w += __shfl_xor_sync(FULL_MASK, acc.w, off);
                 }
                 if (slot == 0 && active) {
-                    if (t.small) st_y4(p.y + (int64_t)(t.row0 + r) * p.ldy + col, acc, pol.stream);
+                    if (t.small) st_y4(p.y + (int64_t)(t.row0 + r) * p.ldy + col, relu4(acc, p.relu), pol.stream);
                     else *reinterpret_cast<float4 *>(&s_part[w][col]) = acc;
                 }
             }
@@ -227,7 +234,7 @@ spmm_units_kernel(const SpmmParams p)
             for (int k = 0; k < SPMM_SCALAR_COLS; k++) {
                 const int c = lane + 32 * k;
                 if (c < p.dim) {
-                    if (t.small) st_y1(p.y + (int64_t)(t.row0 + r) * p.ldy + c, acc[k], pol.stream);
+                    if (t.small) st_y1(p.y + (int64_t)(t.row0 + r) * p.ldy + c, relu1(acc[k], p.relu), pol.stream);
                     else s_part[w][c] = acc[k];
                 }
             }
@@ -246,8 +253,9 @@ spmm_units_kernel(const SpmmParams p)
     const int2 uc = __ldg(p.unit_carry + blockIdx.x);
     const bool enters = w == 0 && uc.x >= 0;            // the row began in an earlier unit
     const bool leaves = w_end - 1 == w_last && uc.y >= 0;   // the row goes on in the next unit
-    float *dst = (enters || leaves) ? p.carry + (int64_t)(enters ? uc.x : uc.y) * SPMM_PANEL
-                                    : p.y + (int64_t)t.row0 * p.ldy;
+    const bool partial = enters || leaves;     // the row is finished by spmm_carry_kernel
+    float *dst = partial ? p.carry + (int64_t)(enters ? uc.x : uc.y) * SPMM_PANEL : p.y + (int64_t)t.row0 * p.ldy;
+    const int act = partial ? 0 : p.relu;
     if (VEC) {
         if (slot == 0 && active) {
             float4 sum = *reinterpret_cast<const float4 *>(&s_part[w][col]);
@@ -255,13 +263,13 @@ spmm_units_kernel(const SpmmParams p)
                 const float4 v = *reinterpret_cast<const float4 *>(&s_part[ww][col]);
                 sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
             }
-            *reinterpret_cast<float4 *>(dst + col) = sum;
+            *reinterpret_cast<float4 *>(dst + col) = relu4(sum, act);
         }
     } else {
         for (int c = lane; c < p.dim; c += 32) {
             float sum = s_part[w][c];
             for (int ww = w + 1; ww < w_end; ww++) sum += s_part[ww][c];
-            dst[c] = sum;
+            dst[c] = relu1(sum, act);
         }
     }
 }
@@ -272,7 +280,7 @@ spmm_units_kernel(const SpmmParams p)
 template <bool VEC>
 __global__ void __launch_bounds__(SPMM_THREADS)
 spmm_carry_kernel(const float *__restrict__ carry, const int *__restrict__ carry_row, int64_t n_carry,
-                  float *__restrict__ y, int64_t ldy, int dim)
+                  float *__restrict__ y, int64_t ldy, int dim, int relu)
 {
     const int64_t s = (int64_t)blockIdx.x * SPMM_WARPS + warp_id();
     if (s >= n_carry) return;
@@ -289,13 +297,13 @@ spmm_carry_kernel(const float *__restrict__ carry, const int *__restrict__ carry
                 const float4 v = *reinterpret_cast<const float4 *>(carry + q * SPMM_PANEL + col);
                 sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
             }
-            *reinterpret_cast<float4 *>(y + (int64_t)row * ldy + col) = sum;
+            *reinterpret_cast<float4 *>(y + (int64_t)row * ldy + col) = relu4(sum, relu);
         }
     } else {
         for (int c = lane; c < dim; c += 32) {
             float sum = carry[s * SPMM_PANEL + c];
             for (int64_t q = s + 1; q < s_end; q++) sum += carry[q * SPMM_PANEL + c];
-            y[(int64_t)row * ldy + c] = sum;
+            y[(int64_t)row * ldy + c] = relu1(sum, relu);
         }
     }
 }

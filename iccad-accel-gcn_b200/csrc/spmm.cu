@@ -128,8 +128,9 @@ static int env_int(const char *name, int dflt)
 }
 
 static int spmm_run(agcn_spmm_plan *p, const int *d_indices, const float *d_vals, const float *d_x, int64_t ldx,
-                    float *d_y, int64_t ldy, int dim, cudaStream_t s)
+                    float *d_y, int64_t ldy, int dim, cudaStream_t s, int activation = 0)
 {
+    AGCN_REQUIRE(activation == 0 || activation == 1, "agcn_spmm_run_act: activation must be AGCN_ACT_NONE or AGCN_ACT_RELU");
     AGCN_REQUIRE(p != nullptr, "agcn_spmm_run: null plan");
     AGCN_REQUIRE(d_x != nullptr && d_y != nullptr, "agcn_spmm_run: null X or Y");
     AGCN_REQUIRE(p->nnz == 0 || (d_indices != nullptr && d_vals != nullptr), "agcn_spmm_run: null indices or values");
@@ -168,6 +169,7 @@ static int spmm_run(agcn_spmm_plan *p, const int *d_indices, const float *d_vals
         prm.unit_carry = p->unit_carry; prm.carry = p->carry;
         prm.zero_rows = p->zero_rows; prm.n_zero_rows = p->n_zero;
         prm.l2_hints = hints;
+        prm.relu = activation;
         const bool vec = width % 4 == 0 && ldx % 4 == 0 && ldy % 4 == 0 && aligned16(prm.x) && aligned16(prm.y);
         if (grid > 0) {
             if (!vec) launch_units<0>(prm, (unsigned)grid, unroll, s);
@@ -181,7 +183,7 @@ static int spmm_run(agcn_spmm_plan *p, const int *d_indices, const float *d_vals
         if (p->n_carry > 0) {
             const unsigned cgrid = (unsigned)ceil_div(p->n_carry, SPMM_WARPS);
             auto k = vec ? spmm_carry_kernel<true> : spmm_carry_kernel<false>;
-            AGCN_KERNEL(k, cgrid, SPMM_THREADS, s, (const float *)p->carry, (const int *)p->carry_row, p->n_carry, prm.y, ldy, width);
+            AGCN_KERNEL(k, cgrid, SPMM_THREADS, s, (const float *)p->carry, (const int *)p->carry_row, p->n_carry, prm.y, ldy, width, activation);
             AGCN_LAUNCH_CHECK("spmm_carry_kernel");
             p->launches_last_run++;
         }
@@ -203,6 +205,14 @@ extern "C" int agcn_spmm_run(agcn_spmm_plan *plan, const int32_t *d_indices, con
 {
     agcn::clear_error();
     return agcn::spmm_run(plan, d_indices, d_vals, d_x, ldx, d_y, ldy, dim, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int agcn_spmm_run_act(agcn_spmm_plan *plan, const int32_t *d_indices, const float *d_vals,
+                                 const float *d_x, int64_t ldx, float *d_y, int64_t ldy, int dim, int activation,
+                                 void *stream)
+{
+    agcn::clear_error();
+    return agcn::spmm_run(plan, d_indices, d_vals, d_x, ldx, d_y, ldy, dim, static_cast<cudaStream_t>(stream), activation);
 }
 
 extern "C" int agcn_spmm_destroy(agcn_spmm_plan *plan)

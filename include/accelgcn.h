@@ -142,12 +142,31 @@ int agcn_spmm_create(agcn_spmm_plan **plan, const int32_t *d_block4, int64_t n_b
 int agcn_spmm_run(agcn_spmm_plan *plan, const int32_t *d_indices, const float *d_vals,
                   const float *d_x, int64_t ldx, float *d_y, int64_t ldy, int dim, void *stream);
 
+/* agcn_spmm_run with a fused element-wise activation on Y (the aggregation step of a GCN layer,
+ * relu(A * Z)).  The reference kernel has no epilogue; AGCN_ACT_NONE is agcn_spmm_run. */
+#define AGCN_ACT_NONE 0
+#define AGCN_ACT_RELU 1
+int agcn_spmm_run_act(agcn_spmm_plan *plan, const int32_t *d_indices, const float *d_vals,
+                      const float *d_x, int64_t ldx, float *d_y, int64_t ldy, int dim, int activation,
+                      void *stream);
+
 int agcn_spmm_destroy(agcn_spmm_plan *plan);
 
 /* Number of kernel launches the last agcn_spmm_run on this plan issued, and
  * the sizes of its internal scratch (for reporting). */
 int agcn_spmm_plan_info(const agcn_spmm_plan *plan, int64_t *n_units, int64_t *n_carry,
                         int64_t *n_zero_rows, int *launches_last_run);
+
+/* ------------------------------------------------------------------------
+ * Dense feature transform of a GCN layer:  Z[m_rows x n_dim] = H[m_rows x k_dim] * W[k_dim x n_dim],
+ * row-major fp32 operands, TF32 multiply with fp32 accumulation on the tensor cores (tcgen05).
+ * The reference benchmarks the SpMM alone and has no dense transform; this is the X*W step that
+ * surrounds it in a GCN layer.  Only k_dim = n_dim = 128 is built (other sizes: AGCN_ERR_INVALID).
+ * ldh / ldz are row strides in floats (>= 128, multiples of 4); W is contiguous.  H and Z must be
+ * 16-byte aligned and must not overlap.  The call returns after the product has completed.
+ * ---------------------------------------------------------------------- */
+int agcn_gemm_tf32(const float *d_h, int64_t ldh, const float *d_w, float *d_z, int64_t ldz,
+                   int64_t m_rows, int k_dim, int n_dim, void *stream);
 
 /* ------------------------------------------------------------------------
  * Host-buffer SpMM: the plug-in used by a harness that keeps its arrays in
