@@ -41,7 +41,12 @@ WORKLOADS = {
     "cfg3": (3, 1.0, (64,)),
     "cfg4": (4, 1.0, tuple(range(16, 129, 4))),
     "cfg2-small": (2, 0.04, (32, 64, 128)),      # for quick checks of the script itself
+    # two-layer GCN forward relu(A relu(A X W1) W2), 128 features (step = one forward)
+    "cfg5": (5, 1.0, (128,)),
+    "cfg5-5m": (5, 0.1, (128,)),
+    "cfg5-small": (5, 0.002, (128,)),
 }
+GCN_WORKLOADS = ("cfg5", "cfg5-5m", "cfg5-small")
 METRIC, UNIT = "spmm_gflops", "GFLOP/s"
 FALLBACK_HBM_GBS = 6650.0
 NCU_TRAFFIC_BYTES = {("cfg2", 128): 3.781e9}      # (workload, dim) -> DRAM bytes per product, from ncu
@@ -393,6 +398,145 @@ def ours(args, rank, world, local_rank):
     print(json.dumps(line), flush=True)
 
 
+def ours_gcn(args, rank, world, local_rank):
+    """Two-layer GCN forward on the row-sharded operator (configuration 5).  One step = one forward:
+    per layer a TF32 GEMM on the owned rows, an all-gather of the result, the SpMM with fused ReLU."""
+    import torch
+    import torch.distributed as dist
+    from accelgcn import synth, sharded, gcn, _lib
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device: the library has no CPU fallback"
+    _lib.load()
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+
+    def barrier():
+        torch.cuda.synchronize(dev)
+        if world > 1:
+            dist.barrier()
+
+    g, ip, ix, v, _dims = build_workload(args.workload, dev)
+    n, nnz, seed, info = g.n, int(ix.numel()), g.info["seed"], dict(g.info)
+    del g
+    shard = sharded.ShardedSpmm(ip, ix, v, rank, world)
+    ip_h = ip.cpu().numpy() if rank == 0 and world == 1 else None
+    ix_keep, v_keep = (ix, v) if world == 1 else (None, None)
+    del ip, ix, v
+    torch.cuda.empty_cache()
+    r0, r1 = shard.row_range
+    nb = torch.tensor([int(shard.block4.shape[0])], dtype=torch.int64, device=dev)
+    if world > 1:
+        dist.all_reduce(nb)
+    n_blocks = int(nb.item())
+    # this rank's rows of X, generated in slabs (the generator addresses elements by index)
+    x_local = torch.empty((r1 - r0, 128), dtype=torch.float32, device=dev)
+    slab = 4_000_000
+    for a in range(r0, r1, slab):
+        b = min(r1, a + slab)
+        x_local[a - r0:b - r0] = synth.uniform_f32(seed, 7, a * 128, (b - a) * 128, -1.0, 1.0, dev).reshape(b - a, 128)
+    w1, w2 = synth.glorot(128, 128, seed, 8, dev), synth.glorot(128, 128, seed, 9, dev)
+    fwd = gcn.GcnForward(shard, [w1, w2])
+
+    for _ in range(max(args.warmup, 3)):
+        fwd.forward(x_local)
+    barrier()
+    uuid = str(getattr(torch.cuda.get_device_properties(dev), "uuid", ""))
+    sampler = ClockSampler(uuid)
+    timings = []
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        out = fwd.forward(x_local, timings)
+    e1.record()
+    barrier()
+    total_ms = e0.elapsed_time(e1)
+    t_load = time.perf_counter()
+    while total_ms < 1500 and time.perf_counter() - t_load < 1.5 - total_ms / 1e3:
+        fwd.forward(x_local)
+        torch.cuda.synchronize(dev)
+    clocks = sampler.stop()
+    parts = torch.tensor([np.mean([ev[i].elapsed_time(ev[i + 1]) for ev in timings]) for i in range(3)],
+                         dtype=torch.float64, device=dev)          # per layer: gemm, all-gather, spmm
+    t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(parts, op=dist.ReduceOp.MAX)
+    total_ms = float(t.item())
+    gemm_ms, gather_ms, spmm_ms = parts.tolist()
+    flops_step = 2 * (2.0 * nnz * 128 + 2.0 * n * 128 * 128)
+    value = flops_step * args.steps / (total_ms / 1e3) / 1e9
+
+    # end to end: X rows up from pinned host memory, forward, output rows down
+    hx = x_local.cpu().pin_memory()
+    hy = torch.empty((r1 - r0, 128), dtype=torch.float32).pin_memory()
+    xd = torch.empty_like(x_local)
+
+    def e2e_step():
+        xd.copy_(hx, non_blocking=True)
+        hy.copy_(fwd.forward(xd), non_blocking=True)
+        torch.cuda.synchronize(dev)
+
+    e2e_steps = max(1, min(args.steps, 3))
+    e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    barrier()
+    e2e_s = torch.tensor([time.perf_counter() - t0], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(e2e_s, op=dist.ReduceOp.MAX)
+    e2e_value = flops_step * e2e_steps / float(e2e_s.item()) / 1e9
+    same = bool(torch.equal(hy, out.cpu()))
+    if rank != 0:
+        dist.destroy_process_group()
+        return
+
+    peak, peak_src = hbm_peak()
+    n_loc = r1 - r0
+    gemm_bytes = 2 * 4 * 128 * n_loc + 4 * 128 * 128                       # H read + Z written (+ W)
+    spmm_bytes = min_bytes(int(shard.indices.numel()), int(shard.block4.shape[0]), n_loc, n, 128)
+    line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": total_ms / args.steps, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32 (SpMM), tf32 multiply / f32 accumulate (X*W)",
+            "data": "synthetic",
+            "config": {"workload": f"{args.workload}: two-layer GCN forward relu(A relu(A X W1) W2) on synthetic config 5, "
+                                   f"N={n}, nnz={nnz}, max degree {info['max_degree']}, {n_blocks} .block4 tuples, 128 features, "
+                                   f"A row-sharded by nonzeros over {world} GPU(s), all-gather of X*W per layer",
+                       "n": n, "nnz": nnz, "n_blocks": n_blocks, "l2": "no flush: every operand is larger than L2"},
+            "per_layer_ms": {"gemm": gemm_ms, "all_gather": gather_ms, "spmm_relu": spmm_ms},
+            "roofline": {"bound": "hbm", "achieved": spmm_bytes / spmm_ms / 1e6, "peak": peak, "unit": "GB/s",
+                         "frac": spmm_bytes / spmm_ms / 1e6 / peak, "traffic": None, "peak_source": peak_src,
+                         "kernel": "spmm_units_kernel dim=128 (+ReLU), per rank",
+                         "algorithmic_bytes_per_launch": spmm_bytes,
+                         "gemm": {"kernel": "gemm_tf32_128_kernel", "achieved": gemm_bytes / gemm_ms / 1e6,
+                                  "frac": gemm_bytes / gemm_ms / 1e6 / peak, "algorithmic_bytes_per_launch": gemm_bytes}},
+            "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 4 * 128 * n_loc, "d2h_bytes_per_step": 4 * 128 * n_loc,
+                    "steps": e2e_steps, "bit_identical_to_resident_run": same},
+            "gpu_launches": args.steps * 2 * (1 + shard.plan.info()["launches_last_run"]),
+            "plan": shard.plan.info()}
+    if world == 1:
+        # CPU baseline on a bounded sample: every k-th row of A (SpMM) and of H (X*W, numpy/BLAS)
+        from oracle import oracle
+        ix_h, v_h = ix_keep.cpu().numpy(), v_keep.cpu().numpy()
+        x_h = x_local.cpu().numpy()
+        gf, dt, desc, stride = cpu_spmm_rate(ip_h, ix_h, v_h, [x_h], args.cpu_seconds)
+        rows = x_h[::stride]
+        t0 = time.perf_counter()
+        rows @ w1.cpu().numpy()
+        dt_g = time.perf_counter() - t0
+        samp_flops = 2.0 * (nnz / stride) * 128 + 2.0 * len(rows) * 128 * 128
+        line["cpu_baseline"] = {"value": samp_flops / (dt + dt_g) / 1e9, "unit": UNIT, "cores": oracle.num_threads(),
+                                "kind": "port", "sample": "one layer (X*W then A*Z) on " + desc, "seconds": dt + dt_g}
+    else:
+        dist.destroy_process_group()
+    print(json.dumps(line), flush=True)
+
+
 def reference_gpu_kernels(block4, ip_h, ix_h, v_h, xs_h, dims, nnz):
     """The reference's own spmm_accel kernel and its cuSPARSE call, compiled from the reference
     sources (oracle/_ref), timed on this GPU with the reference's own protocol (mean wall-clock
@@ -428,6 +572,8 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         reference_arm(args, rank, world)
+    elif args.workload in GCN_WORKLOADS:
+        ours_gcn(args, rank, world, local_rank)
     else:
         ours(args, rank, world, local_rank)
 

@@ -142,17 +142,21 @@ static int spmm_run(agcn_spmm_plan *p, const int *d_indices, const float *d_vals
     AGCN_REQUIRE(grid < (int64_t)INT32_MAX, "agcn_spmm_run: grid too large");
     // Column panels.  The gather re-reads a row of X once per nonzero of that column, so it runs
     // at L2 speed only while the X columns of a pass stay L2-resident.  When dim > 64 and the
-    // operand is larger than what L2 keeps, two 64-column passes (each re-streaming the 8 bytes
-    // per nonzero of A) beat one 128-column pass that spills to HBM (measured on B200: 3.9 ms
-    // against 4.2-4.7 ms at N = 250 000, dim 128).  Passes stay multiples of 32 columns so that
-    // every row segment is whole 128-byte lines.  AGCN_SPMM_PANEL overrides the choice.
+    // operand is somewhat larger than what L2 keeps, two 64-column passes (each re-streaming the
+    // 8 bytes per nonzero of A) beat one 128-column pass that spills to HBM (measured on B200:
+    // 3.8 ms against 4.2-4.7 ms at N = 250 000, dim 128; 0.77 against 0.86 ms at N = 500 000).
+    // When X is many times larger than L2 neither pass fits and one pass is as fast or faster
+    // (6.3 against 6.5 ms at N = 5 000 000), so the split is limited to operands up to 4x L2.
+    // Passes stay multiples of 32 columns so that every row segment is whole 128-byte lines.
+    // AGCN_SPMM_PANEL overrides the choice.
     int panel = SPMM_PANEL;
     if (dim > 64 && dim % 32 == 0 && ldx % 32 == 0) {
         int dev = 0, l2_bytes = 0;
         AGCN_CUDA(cudaGetDevice(&dev));
         AGCN_CUDA(cudaDeviceGetAttribute(&l2_bytes, cudaDevAttrL2CacheSize, dev));
         const int full = dim < SPMM_PANEL ? dim : SPMM_PANEL;
-        if ((double)p->n_cols * full * 4.0 > 0.75 * (double)l2_bytes) panel = 64;
+        const double x_bytes = (double)p->n_cols * full * 4.0;
+        if (x_bytes > 0.75 * (double)l2_bytes && x_bytes <= 4.0 * (double)l2_bytes) panel = 64;
     }
     panel = env_int("AGCN_SPMM_PANEL", panel);
     AGCN_REQUIRE(panel >= 1 && panel <= SPMM_PANEL, "agcn_spmm_run: AGCN_SPMM_PANEL must be 1..%d", SPMM_PANEL);
