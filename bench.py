@@ -19,6 +19,7 @@ the dense operand (strong scaling: the total work is fixed).
 from __future__ import annotations
 
 import argparse
+import datetime
 import json
 import os
 import subprocess
@@ -224,7 +225,7 @@ def ours(args, rank, world, local_rank):
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
     if world > 1:
-        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev, timeout=datetime.timedelta(seconds=120))
 
     def barrier():
         torch.cuda.synchronize(dev)
@@ -274,18 +275,18 @@ def ours(args, rank, world, local_rank):
         step(evs[k])
     e1.record()
     barrier()
-    total_ms = e0.elapsed_time(e1)
-    # keep the same load running (untimed) until the clock sampler has seen about 1.5 s of it
-    t_load = time.perf_counter()
-    while total_ms < 1500 and time.perf_counter() - t_load < 1.5 - total_ms / 1e3:
+    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    # keep the same load running (untimed) until the clock sampler has seen about 1.5 s of it; the
+    # number of extra steps comes from the reduced time, so every rank runs the same collectives
+    for _ in range(int(max(0.0, 1500.0 - float(t.item())) / max(float(t.item()) / args.steps, 1e-3))):
         step()
-        torch.cuda.synchronize(dev)
+    torch.cuda.synchronize(dev)
     clocks = sampler.stop()
-    t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
     per_dim_ms = torch.tensor([np.mean([evs[k][di][0].elapsed_time(evs[k][di][1]) for k in range(args.steps)])
                                for di in range(len(dims))], dtype=torch.float64, device=dev)
     if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
         dist.all_reduce(per_dim_ms, op=dist.ReduceOp.MAX)
     total_ms = float(t.item())
     per_dim_ms = per_dim_ms.tolist()
@@ -308,8 +309,6 @@ def ours(args, rank, world, local_rank):
     hx, hy = {}, {}
     for d in dims:
         full = synth.features(n, d, g.info["seed"], dev)
-        if world > 1:       # the host call takes the dense operand in the shard's padded numbering
-            full = sharded.all_gather_padded(full[r0:r1].contiguous(), shard.max_rows, world)
         hx[d] = full.cpu().pin_memory()
         hy[d] = torch.empty((r1 - r0, d), dtype=torch.float32).pin_memory()
         del full
@@ -410,7 +409,7 @@ def ours_gcn(args, rank, world, local_rank):
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
     if world > 1:
-        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev, timeout=datetime.timedelta(seconds=120))
 
     def barrier():
         torch.cuda.synchronize(dev)
@@ -452,17 +451,16 @@ def ours_gcn(args, rank, world, local_rank):
         out = fwd.forward(x_local, timings)
     e1.record()
     barrier()
-    total_ms = e0.elapsed_time(e1)
-    t_load = time.perf_counter()
-    while total_ms < 1500 and time.perf_counter() - t_load < 1.5 - total_ms / 1e3:
-        fwd.forward(x_local)
-        torch.cuda.synchronize(dev)
+    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    for _ in range(int(max(0.0, 1500.0 - float(t.item())) / max(float(t.item()) / args.steps, 1e-3))):
+        fwd.forward(x_local)           # same count on every rank (it comes from the reduced time)
+    torch.cuda.synchronize(dev)
     clocks = sampler.stop()
     parts = torch.tensor([np.mean([ev[i].elapsed_time(ev[i + 1]) for ev in timings]) for i in range(3)],
                          dtype=torch.float64, device=dev)          # per layer: gemm, all-gather, spmm
-    t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
     if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
         dist.all_reduce(parts, op=dist.ReduceOp.MAX)
     total_ms = float(t.item())
     gemm_ms, gather_ms, spmm_ms = parts.tolist()

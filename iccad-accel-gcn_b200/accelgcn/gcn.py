@@ -34,8 +34,8 @@ class GcnForward:
             z = gemm.gemm_tf32(h, w, out=self._buf("z", sh.n_local, w.shape[1], h))
             if ev: ev[1].record()
             if sh.world > 1:
-                zg = sharded.all_gather_padded(z, sh.max_rows, sh.world,
-                                               out=self._buf("zg", sh.n_cols, w.shape[1], h), group=sh.group)
+                zg = sharded.all_gather_rows(z, sh.cuts, sh.rank, sh.world,
+                                             out=self._buf("zg", sh.n_cols, w.shape[1], h), group=sh.group)
             else:
                 zg = z
             if ev: ev[2].record()

@@ -8,10 +8,10 @@ pointers -- the format is unchanged, row and nonzero offsets are shard-local)
 and the same rows of the dense operand.  One step is: all-gather the dense
 operand (the only exchange the path has), then the local SpMM.
 
-All ranks' dense rows are gathered into one padded buffer of
-world_size * max_rows rows, so the collective is a single equal-sized
-all-gather even though the shards hold different numbers of rows; the column
-ids of each shard are renumbered once, at set-up, to positions in that buffer.
+Balancing by nonzeros makes the row counts very uneven (the first rank owns
+most of the light rows), so the exchange is an all-gather with a different
+block size per rank, straight into the [n x dim] operand in global row order:
+nothing is padded and column ids keep their global numbering.
 
 The reference has no multi-GPU code; this follows its single-GPU operator
 (spmm_accel.cu) shard by shard.
@@ -34,19 +34,6 @@ def nnz_balanced_cuts(indptr, n_parts: int) -> np.ndarray:
     return np.maximum.accumulate(cuts)
 
 
-def padded_position(cols, cuts, max_rows: int):
-    """Global row id -> row of the padded all-gather buffer (rank * max_rows + local row).
-    Works on numpy arrays and torch tensors alike."""
-    is_np = isinstance(cols, np.ndarray)
-    if is_np:
-        owner = np.searchsorted(cuts[1:-1], cols, side="right")
-        return (owner * max_rows + (cols - np.asarray(cuts)[owner])).astype(cols.dtype)
-    import torch
-    c = torch.as_tensor(np.asarray(cuts), device=cols.device)
-    owner = torch.searchsorted(c[1:-1].contiguous(), cols.to(torch.int64), right=True)
-    return (owner * max_rows + (cols.to(torch.int64) - c[owner])).to(cols.dtype)
-
-
 def shard_rows(indptr, indices, vals, cuts, rank: int):
     """The rows [cuts[rank], cuts[rank+1]) of a CSR matrix, row pointers rebased to 0."""
     r0, r1 = int(cuts[rank]), int(cuts[rank + 1])
@@ -54,24 +41,26 @@ def shard_rows(indptr, indices, vals, cuts, rank: int):
     return indptr[r0:r1 + 1] - indptr[r0], indices[p0:p1], vals[p0:p1]
 
 
-def all_gather_padded(x_local, max_rows: int, world_size: int, out=None, group=None):
-    """All-gather the ranks' row blocks (each at most max_rows rows) into one
-    [world_size * max_rows, dim] buffer.  Rows past a rank's own count are
-    padding and are never referenced by a renumbered column id."""
+def all_gather_rows(x_local, cuts, rank: int, world_size: int, out=None, group=None):
+    """All-gather row blocks of different heights: rank r contributes rows [cuts[r], cuts[r+1]) of
+    the [n x dim] result.  On NCCL this is one all-gather call with per-rank sizes (grouped
+    broadcasts inside the library); on other backends (the gloo CPU tests) one broadcast per rank."""
     import torch
     import torch.distributed as dist
-    dim = x_local.shape[1]
+    n, dim = int(cuts[-1]), x_local.shape[1]
     if out is None:
-        out = torch.empty((world_size * max_rows, dim), dtype=x_local.dtype, device=x_local.device)
-    if x_local.shape[0] == max_rows and x_local.is_contiguous():
-        send = x_local
-    else:
-        send = torch.zeros((max_rows, dim), dtype=x_local.dtype, device=x_local.device)
-        send[: x_local.shape[0]] = x_local
+        out = torch.empty((n, dim), dtype=x_local.dtype, device=x_local.device)
     if world_size == 1:
-        out.copy_(send)
+        out.copy_(x_local)
+        return out
+    blocks = [out[int(cuts[r]):int(cuts[r + 1])] for r in range(world_size)]
+    if dist.get_backend(group) == "nccl":
+        dist.all_gather(blocks, x_local.contiguous(), group=group)
     else:
-        dist.all_gather_into_tensor(out, send, group=group)
+        blocks[rank].copy_(x_local)
+        for r in range(world_size):
+            if blocks[r].numel():
+                dist.broadcast(blocks[r], src=dist.get_global_rank(group, r) if group is not None else r, group=group)
     return out
 
 
@@ -88,13 +77,12 @@ class ShardedSpmm:
         self.rank, self.world, self.group = rank, world_size, group
         self.n = indptr.numel() - 1
         self.cuts = nnz_balanced_cuts(indptr.cpu().numpy(), world_size)
-        self.max_rows = int(np.diff(self.cuts).max())
         ip, ix, v = shard_rows(indptr, indices, vals, self.cuts, rank)
         self.indptr = ip.contiguous()
         self.vals = v.contiguous()
-        self.indices = padded_position(ix.contiguous(), self.cuts, self.max_rows) if world_size > 1 else ix.contiguous()
+        self.indices = ix.contiguous()
         self.n_local = self.indptr.numel() - 1
-        self.n_cols = world_size * self.max_rows if world_size > 1 else self.n
+        self.n_cols = self.n
         self.block4 = partition.block_level_partition_device(self.indptr)
         self.plan = spmm.SpmmPlan(self.block4, self.indices, self.n_local, self.n_cols)
         self._gather = {}
@@ -107,7 +95,7 @@ class ShardedSpmm:
 
     def step(self, x_local, y_local, x_gathered=None):
         """y_local[n_local x dim] = A_shard @ allgather(x_local).  Asynchronous on the current stream.
-        x_gathered, if given, is an already gathered padded operand (the collective is skipped)."""
+        x_gathered, if given, is the already gathered [n x dim] operand (the collective is skipped)."""
         dim = y_local.shape[1]
         if x_gathered is not None:
             x_full = x_gathered
@@ -118,7 +106,7 @@ class ShardedSpmm:
             if buf is None:
                 buf = self._torch.empty((self.n_cols, dim), dtype=x_local.dtype, device=self.device)
                 self._gather[dim] = buf
-            x_full = all_gather_padded(x_local, self.max_rows, self.world, out=buf, group=self.group)
+            x_full = all_gather_rows(x_local, self.cuts, self.rank, self.world, out=buf, group=self.group)
         self.plan.run(self.indices, self.vals, x_full, y_local, dim=dim, ldx=dim, ldy=dim)
         return y_local
 

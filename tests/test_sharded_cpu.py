@@ -1,5 +1,5 @@
-"""Host-side logic of the row-sharded path on CPU: nnz-balanced cuts, column renumbering and
-the padded all-gather over the gloo backend with two ranks.  The arithmetic of a shard is
+"""Host-side logic of the row-sharded path on CPU: nnz-balanced cuts, row shards and the
+uneven all-gather over the gloo backend with two and three ranks.  The arithmetic of a shard is
 checked with the CPU oracle here; the GPU kernels are covered by the -m gpu tests."""
 import os
 import socket
@@ -42,17 +42,6 @@ def test_cuts_degenerate_inputs():
     assert sharded.nnz_balanced_cuts(np.array([0, 10]), 3).tolist()[-1] == 1
 
 
-def test_padded_position_is_consistent_with_the_gather_layout():
-    from accelgcn import sharded
-    cuts = np.array([0, 5, 6, 20])
-    max_rows = 14
-    cols = np.arange(20, dtype=np.int32)
-    pos = sharded.padded_position(cols, cuts, max_rows)
-    assert pos[:5].tolist() == [0, 1, 2, 3, 4] and pos[5] == 14 and pos[6] == 28 and pos[19] == 41
-    pos_t = sharded.padded_position(torch.from_numpy(cols), cuts, max_rows)
-    assert pos_t.dtype == torch.int32 and pos_t.tolist() == pos.tolist()
-
-
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
@@ -68,11 +57,10 @@ def _worker(rank, world, port, dim, result_dir):
         n = len(indptr) - 1
         x = np.random.default_rng(7).uniform(-1, 1, (n, dim)).astype(np.float32)
         cuts = sharded.nnz_balanced_cuts(indptr, world)
-        max_rows = int(np.diff(cuts).max())
         ip, ix, v = sharded.shard_rows(indptr, idx, val, cuts, rank)
-        ix = sharded.padded_position(ix, cuts, max_rows)
         r0, r1 = int(cuts[rank]), int(cuts[rank + 1])
-        x_full = sharded.all_gather_padded(torch.from_numpy(x[r0:r1]), max_rows, world).numpy()
+        x_full = sharded.all_gather_rows(torch.from_numpy(x[r0:r1].copy()), cuts, rank, world).numpy()
+        assert np.array_equal(x_full, x)          # uneven blocks land in global row order
         # the shard's own .block4 and product, computed by the oracle (this is a CPU test)
         y = oracle.spmm_block4(oracle.partition(ip), ix, v, x_full, r1 - r0)
         np.save(os.path.join(result_dir, f"y{rank}.npy"), y)

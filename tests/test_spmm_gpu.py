@@ -237,7 +237,7 @@ def test_parity_with_the_reference_kernel_heavy_rows(cfg4_small):
 @pytest.mark.parametrize("world", [2, 5])
 def test_row_sharded_product_on_one_gpu_equals_unsharded(cfg4_small, world):
     # every rank's shard built and multiplied in this one process (the all-gather is replaced by
-    # assembling the padded operand by hand): shard-local .block4, renumbered columns, padded X
+    # handing over the full operand): shard-local .block4 and row offsets, global column ids
     import torch
     from accelgcn import sharded
     c = cfg4_small
@@ -247,10 +247,7 @@ def test_row_sharded_product_on_one_gpu_equals_unsharded(cfg4_small, world):
     parts = []
     for r in range(world):
         sh = sharded.ShardedSpmm(ip, ix, v, r, world)
-        xg = torch.zeros((world * sh.max_rows, 64), dtype=torch.float32, device=dev)
-        for q in range(world):
-            q0, q1 = int(sh.cuts[q]), int(sh.cuts[q + 1])
-            xg[q * sh.max_rows: q * sh.max_rows + (q1 - q0)] = torch.from_numpy(x[q0:q1]).to(dev)
+        xg = torch.from_numpy(x).to(dev)              # what the all-gather assembles: X in global row order
         y = torch.full((sh.n_local, 64), float("nan"), dtype=torch.float32, device=dev)
         sh.step(None, y, x_gathered=xg)
         torch.cuda.synchronize()
