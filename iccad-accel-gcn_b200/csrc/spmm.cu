@@ -114,10 +114,9 @@ static int spmm_create(agcn_spmm_plan **out, const int *d_block4, int64_t n_bloc
 }
 
 template <int S>
-static void launch_units(const SpmmParams &prm, unsigned grid, int unroll, cudaStream_t s)
+static void launch_units(const SpmmParams &prm, unsigned grid, cudaStream_t s)
 {
-    (void)unroll;
-    auto k = spmm_units_kernel<S, 8>;
+    auto k = spmm_units_kernel<S>;
     AGCN_KERNEL(k, grid, SPMM_THREADS, s, prm);
 }
 
@@ -160,7 +159,6 @@ static int spmm_run(agcn_spmm_plan *p, const int *d_indices, const float *d_vals
     }
     panel = env_int("AGCN_SPMM_PANEL", panel);
     AGCN_REQUIRE(panel >= 1 && panel <= SPMM_PANEL, "agcn_spmm_run: AGCN_SPMM_PANEL must be 1..%d", SPMM_PANEL);
-    const int unroll = 8;
     const int hints = 3;      // keep X in L2, stream A and Y through it
     for (int col0 = 0; col0 < dim; col0 += panel) {
         const int width = dim - col0 < panel ? dim - col0 : panel;
@@ -176,11 +174,11 @@ static int spmm_run(agcn_spmm_plan *p, const int *d_indices, const float *d_vals
         prm.relu = activation;
         const bool vec = width % 4 == 0 && ldx % 4 == 0 && ldy % 4 == 0 && aligned16(prm.x) && aligned16(prm.y);
         if (grid > 0) {
-            if (!vec) launch_units<0>(prm, (unsigned)grid, unroll, s);
-            else if (width <= 16) launch_units<4>(prm, (unsigned)grid, unroll, s);
-            else if (width <= 32) launch_units<8>(prm, (unsigned)grid, unroll, s);
-            else if (width <= 64) launch_units<16>(prm, (unsigned)grid, unroll, s);
-            else launch_units<32>(prm, (unsigned)grid, unroll, s);
+            if (!vec) launch_units<0>(prm, (unsigned)grid, s);
+            else if (width <= 16) launch_units<4>(prm, (unsigned)grid, s);
+            else if (width <= 32) launch_units<8>(prm, (unsigned)grid, s);
+            else if (width <= 64) launch_units<16>(prm, (unsigned)grid, s);
+            else launch_units<32>(prm, (unsigned)grid, s);
             AGCN_LAUNCH_CHECK("spmm_units_kernel");
             p->launches_last_run++;
         }
