@@ -51,7 +51,7 @@ WORKLOADS = {
 GCN_WORKLOADS = ("cfg5", "cfg5-5m", "cfg5-1m", "cfg5-small")
 METRIC, UNIT = "spmm_gflops", "GFLOP/s"
 FALLBACK_HBM_GBS = 6650.0
-NCU_TRAFFIC_BYTES = {("cfg2", 128): 3.781e9}      # (workload, dim) -> DRAM bytes per product, from ncu
+NCU_TRAFFIC_BYTES = {("cfg2", 128): 4.070e9}      # (workload, dim) -> DRAM bytes per product, from ncu
 
 
 def hbm_peak():
