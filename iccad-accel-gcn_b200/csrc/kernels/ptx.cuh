@@ -28,18 +28,10 @@ __device__ __forceinline__ L2Policies make_l2_policies()
     return p;
 }
 
-__device__ __forceinline__ uint64_t make_l2_policy_normal()
-{
-    uint64_t p;
-    asm("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(p));
-    return p;
-}
-
 // dense operand X: read-only path, 16 bytes per lane, keep in L2
 __device__ __forceinline__ float4 ld_x4(const float *p, uint64_t policy)
 {
     float4 v;
-    if (policy == 0) return __ldg(reinterpret_cast<const float4 *>(p));
     asm("ld.global.nc.L2::cache_hint.v4.f32 {%0, %1, %2, %3}, [%4], %5;"
                  : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p), "l"(policy));
     return v;
@@ -55,14 +47,12 @@ __device__ __forceinline__ float ld_x1(const float *p, uint64_t policy)
 __device__ __forceinline__ int ld_a(const int *p, uint64_t policy)
 {
     int v;
-    if (policy == 0) return __ldg(p);
     asm("ld.global.nc.L1::no_allocate.L2::cache_hint.s32 %0, [%1], %2;" : "=r"(v) : "l"(p), "l"(policy));
     return v;
 }
 __device__ __forceinline__ float ld_a(const float *p, uint64_t policy)
 {
     float v;
-    if (policy == 0) return __ldg(p);
     asm("ld.global.nc.L1::no_allocate.L2::cache_hint.f32 %0, [%1], %2;" : "=f"(v) : "l"(p), "l"(policy));
     return v;
 }
@@ -70,7 +60,6 @@ __device__ __forceinline__ float ld_a(const float *p, uint64_t policy)
 // result rows: written once
 __device__ __forceinline__ void st_y4(float *p, const float4 &v, uint64_t policy)
 {
-    if (policy == 0) { *reinterpret_cast<float4 *>(p) = v; return; }
     asm volatile("st.global.L2::cache_hint.v4.f32 [%0], {%1, %2, %3, %4}, %5;"
                  :: "l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w), "l"(policy) : "memory");
 }

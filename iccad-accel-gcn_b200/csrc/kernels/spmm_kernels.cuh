@@ -54,7 +54,6 @@ struct SpmmParams {
     float *carry;             // [n_carry][SPMM_PANEL]
     const int *zero_rows;     // rows no tuple covers
     int64_t n_zero_rows;
-    int l2_hints;             // bit 0: keep X in L2 (evict_last); bit 1: stream A and Y (evict_first)
     int relu;                 // nonzero: Y = max(A * X, 0) (fused GCN activation)
 };
 
@@ -131,21 +130,54 @@ __device__ __forceinline__ float4 gather_vec4(const int2 *pairs, int count, int 
 
 constexpr int SPMM_SCALAR_COLS = SPMM_PANEL / 32;   // columns per lane in scalar mode
 
+// Scalar mode: lane l owns columns l, l+32, ... (K = ceil(dim / 32) of them), every load instruction
+// of the warp reads 128 contiguous bytes of one X row.  Nonzeros are taken in batches so that about
+// 8 loads per lane are in flight, as in the float4 mode.
+template <int K>
+__device__ __forceinline__ void gather_strided(const int2 *pairs, int count, const float *__restrict__ x,
+                                               int64_t ldx, int dim, float (&acc)[SPMM_SCALAR_COLS], uint64_t keep)
+{
+    constexpr int U = K <= 2 ? 4 : 2;        // nonzeros per batch
+    const int lane = lane_id();
+    bool live[K];
+#pragma unroll
+    for (int k = 0; k < K; k++) live[k] = lane + 32 * k < dim;
+#pragma unroll
+    for (int k = 0; k < SPMM_SCALAR_COLS; k++) acc[k] = 0.f;
+    int i = 0;
+    for (; i + U <= count; i += U) {
+        int2 p[U];
+        float v[U][K];
+#pragma unroll
+        for (int u = 0; u < U; u++) p[u] = pairs[i + u];
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const float *xr = x + (int64_t)p[u].x * ldx + lane;
+#pragma unroll
+            for (int k = 0; k < K; k++) v[u][k] = live[k] ? ld_x1(xr + 32 * k, keep) : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < U; u++)
+#pragma unroll
+            for (int k = 0; k < K; k++) acc[k] = fmaf(__int_as_float(p[u].y), v[u][k], acc[k]);
+    }
+    for (; i < count; i++) {
+        const int2 p0 = pairs[i];
+        const float *xr = x + (int64_t)p0.x * ldx + lane;
+#pragma unroll
+        for (int k = 0; k < K; k++)
+            if (live[k]) acc[k] = fmaf(__int_as_float(p0.y), ld_x1(xr + 32 * k, keep), acc[k]);
+    }
+}
+
 __device__ __forceinline__ void gather_scalar(const int2 *pairs, int count, const float *__restrict__ x,
                                               int64_t ldx, int dim, float (&acc)[SPMM_SCALAR_COLS], uint64_t keep)
 {
-    const int lane = lane_id();
-#pragma unroll
-    for (int k = 0; k < SPMM_SCALAR_COLS; k++) acc[k] = 0.f;
-    for (int i = 0; i < count; i++) {
-        const int2 p = pairs[i];
-        const float a = __int_as_float(p.y);
-        const float *xr = x + (int64_t)p.x * ldx;
-#pragma unroll
-        for (int k = 0; k < SPMM_SCALAR_COLS; k++) {
-            const int c = lane + 32 * k;
-            if (c < dim) acc[k] = fmaf(a, ld_x1(xr + c, keep), acc[k]);
-        }
+    switch ((dim + 31) >> 5) {            // uniform over the launch
+    case 1: gather_strided<1>(pairs, count, x, ldx, dim, acc, keep); break;
+    case 2: gather_strided<2>(pairs, count, x, ldx, dim, acc, keep); break;
+    case 3: gather_strided<3>(pairs, count, x, ldx, dim, acc, keep); break;
+    default: gather_strided<4>(pairs, count, x, ldx, dim, acc, keep); break;
     }
 }
 
@@ -170,9 +202,7 @@ spmm_units_kernel(const SpmmParams p)
     const int slot = lane / LANES, sl = lane % LANES;
     const int col = VEC ? sl * 4 : sl;
     const bool active = col < p.dim;
-    L2Policies pol = make_l2_policies();
-    if (!(p.l2_hints & 1)) pol.keep = (p.l2_hints & 4) ? 0 : make_l2_policy_normal();
-    if (!(p.l2_hints & 2)) pol.stream = (p.l2_hints & 4) ? 0 : make_l2_policy_normal();
+    const L2Policies pol = make_l2_policies();
 
     if ((int64_t)blockIdx.x >= p.n_units) {
         // zero-fill rows that no tuple covers

@@ -159,7 +159,6 @@ static int spmm_run(agcn_spmm_plan *p, const int *d_indices, const float *d_vals
     }
     panel = env_int("AGCN_SPMM_PANEL", panel);
     AGCN_REQUIRE(panel >= 1 && panel <= SPMM_PANEL, "agcn_spmm_run: AGCN_SPMM_PANEL must be 1..%d", SPMM_PANEL);
-    const int hints = 3;      // keep X in L2, stream A and Y through it
     for (int col0 = 0; col0 < dim; col0 += panel) {
         const int width = dim - col0 < panel ? dim - col0 : panel;
         SpmmParams prm;
@@ -170,7 +169,6 @@ static int spmm_run(agcn_spmm_plan *p, const int *d_indices, const float *d_vals
         prm.dim = width;
         prm.unit_carry = p->unit_carry; prm.carry = p->carry;
         prm.zero_rows = p->zero_rows; prm.n_zero_rows = p->n_zero;
-        prm.l2_hints = hints;
         prm.relu = activation;
         const bool vec = width % 4 == 0 && ldx % 4 == 0 && ldy % 4 == 0 && aligned16(prm.x) && aligned16(prm.y);
         if (grid > 0) {
