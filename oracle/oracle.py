@@ -30,6 +30,10 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB = None
 
+# Where the reference source tree is looked for when it is needed (building oracle/_ref,
+# regenerating fixtures, the live-script tests); absent on a GPU box, and nothing there needs it.
+REFERENCE_DIR = os.environ.get("ACCELGCN_REFERENCE", os.path.join(os.sep, "root", "reference"))
+
 DEG_BOUND = 12 * 32   # block_level_partition.py:7
 NUM_WARPS = 12        # block_level_partition.py:8
 

@@ -27,6 +27,17 @@ def pytest_collection_modifyitems(config, items):
     items.sort(key=lambda it: os.path.basename(str(it.fspath)).startswith("test_zz_"))
 
 
+@pytest.fixture(scope="session", autouse=True)
+def built_library():
+    """libaccelgcn.so is compiled from csrc/ when it is missing or older than its sources (nvcc
+    cross-compiles without a GPU).  Nothing falls back to anything else if that fails."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("agcn_build", os.path.join(PKG, "build.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod.build()
+
+
 @pytest.fixture(scope="session")
 def kat():
     """Degree sequences and hashes of the 16 golden .block4 files of the reference."""

@@ -1,6 +1,6 @@
 """Regenerates the fixtures in this directory.  Needs the reference source tree
-(default /root/reference, override with ACCELGCN_REFERENCE); the tests
-themselves only read the committed fixtures.
+(its location is oracle.REFERENCE_DIR, settable with ACCELGCN_REFERENCE); the
+tests themselves only read the committed fixtures.
 
     python tests/golden/make_golden.py
 
@@ -26,8 +26,9 @@ import tempfile
 
 import numpy as np
 
-REF = os.environ.get("ACCELGCN_REFERENCE", "/root/reference")
 HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+from oracle.oracle import REFERENCE_DIR as REF  # noqa: E402
 
 
 def invert_block4(b):

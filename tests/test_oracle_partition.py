@@ -8,7 +8,7 @@ import pytest
 from conftest import kat_indptr, sha256_block4
 from oracle import oracle
 
-REFERENCE = os.environ.get("ACCELGCN_REFERENCE", "/root/reference")
+REFERENCE = oracle.REFERENCE_DIR
 
 
 def test_pattern_tables_closed_form():
@@ -78,3 +78,30 @@ def test_degree_sort_oracle_properties():
         o = perm[r]
         assert np.array_equal(nidx[nip[r]:nip[r + 1]], inv[idx[indptr[o]:indptr[o + 1]]])
         assert np.array_equal(nval[nip[r]:nip[r + 1]], val[indptr[o]:indptr[o + 1]])
+
+
+@pytest.mark.skipif(not os.path.isfile(os.path.join(REFERENCE, "block_level_partition.py")), reason="reference tree not present")
+@pytest.mark.parametrize("seed", [0, 1, 2])
+def test_oracle_against_the_unmodified_script_run_live(seed, tmp_path):
+    # fresh random degree sequences through the reference script itself (subprocess, scratch directory
+    # laid out as it expects), not only the committed fixtures
+    import subprocess
+    import sys
+    rng = np.random.default_rng(1000 + seed)
+    cases = {
+        "sorted": np.sort(rng.choice(np.array([0, 1, 2, 3, 30, 32, 33, 64, 65, 96, 97, 128, 129, 191, 192, 384, 385, 800]), 3000)),
+        "unsorted": rng.choice(np.array([0, 1, 1, 2, 12, 33, 100, 191, 192, 400, 1200]), 3000),
+        "runs": np.repeat(rng.integers(1, 200, 200), rng.integers(1, 30, 200)),
+    }
+    os.makedirs(tmp_path / "graphs")
+    for name, deg in cases.items():
+        indptr = np.concatenate([[0], np.cumsum(deg)]).astype(np.int32)
+        (tmp_path / "graphs" / f"{name}.config").write_text("")
+        indptr.tofile(tmp_path / "graphs" / f"{name}.new_indptr")
+        np.zeros(int(indptr[-1]), dtype=np.int32).tofile(tmp_path / "graphs" / f"{name}.new_indices")
+    subprocess.check_call([sys.executable, os.path.join(REFERENCE, "block_level_partition.py")], cwd=tmp_path,
+                          stdout=subprocess.DEVNULL)
+    for name, deg in cases.items():
+        want = np.fromfile(tmp_path / "block_level_meta" / f"{name}.block4", dtype=np.int32).reshape(-1, 4)
+        indptr = np.concatenate([[0], np.cumsum(deg)]).astype(np.int32)
+        assert np.array_equal(oracle.partition(indptr), want), name

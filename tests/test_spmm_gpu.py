@@ -276,3 +276,38 @@ def test_cpp_harness_same_cli_and_output_as_the_reference(cfg1, tmp_path):
     assert "validation pass!" in out.stdout and "validation fail!" not in out.stdout
     lines = [l.split() for l in out.stdout.splitlines() if l.startswith("0/0 synth1 60 ")]
     assert [l[3] for l in lines] == ["cusparse", "accel", "accel_event"] and all(float(l[4]) > 0 for l in lines)
+
+
+def test_graph_without_nonzeros_gives_zeros():
+    # no tuples at all: every row is zero-filled, nothing else is launched
+    import torch
+    from accelgcn import spmm
+    dev = require_cuda()
+    n = 1000
+    b4 = torch.zeros((0, 4), dtype=torch.int32, device=dev)
+    empty_i = torch.zeros(0, dtype=torch.int32, device=dev)
+    empty_v = torch.zeros(0, dtype=torch.float32, device=dev)
+    for dim in (64, 7):
+        x = torch.ones((n, dim), device=dev)
+        y = torch.full((n, dim), float("nan"), device=dev)
+        spmm.spmm(b4, empty_i, empty_v, x, n, out=y)
+        assert torch.equal(y, torch.zeros_like(y))
+
+
+def test_single_heavy_row_spanning_many_units():
+    # one row of 50 000 nonzeros = 131 tuples = 17 units: all of it goes through the carry path
+    import torch
+    from accelgcn import partition, spmm
+    dev = require_cuda()
+    rng = np.random.default_rng(8)
+    n, d = 60_000, 50_000
+    indptr = np.array([0, d], dtype=np.int32)
+    idx = np.sort(rng.choice(n, d, replace=False)).astype(np.int32)
+    val = rng.uniform(0, 1, d).astype(np.float32)
+    x = rng.uniform(-1, 1, (n, 100)).astype(np.float32)
+    b4 = partition.block_level_partition(indptr)
+    assert len(b4) == 131
+    y = spmm.spmm(torch.from_numpy(b4).to(dev), torch.from_numpy(idx).to(dev), torch.from_numpy(val).to(dev),
+                  torch.from_numpy(x).to(dev), 1).cpu().numpy()
+    ref = oracle.spmm_csr(indptr, idx, val, x)
+    assert spmm_close(y, ref, row_abs_scale(indptr, val, x)).all()
