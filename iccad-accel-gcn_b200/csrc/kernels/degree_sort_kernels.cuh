@@ -33,8 +33,16 @@ degree_keys_kernel(const int *__restrict__ indptr, int64_t n_rows, unsigned *__r
         keys[i] = (unsigned)d;
         rows[i] = (int)i;
     }
+    // one atomic per block, not per warp: at 5e7 rows a million same-address atomics cost more than the pass
+    __shared__ int s_max[256 / 32];
     d = warp_reduce(d, OpMax());
-    if (lane_id() == 0 && d > 0) atomicMax(max_deg, d);
+    if (lane_id() == 0) s_max[warp_id()] = d;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int m = 0;
+        for (int w = 0; w < (int)(blockDim.x >> 5); w++) m = m > s_max[w] ? m : s_max[w];
+        if (m > 0) atomicMax(max_deg, m);
+    }
 }
 
 // hist[digit * n_tiles + tile] = number of keys of the tile with that digit
