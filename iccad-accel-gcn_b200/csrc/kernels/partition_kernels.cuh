@@ -153,14 +153,23 @@ part_count_kernel(const int *__restrict__ indptr, int64_t n_rows, const int *__r
     }
 }
 
-// (C) every row that opens tuples writes them at its scanned offset
+// (C) every row that opens tuples writes them at its scanned offset.  A row of degree D > 384 owns
+// ceil(D / 384) tuples -- thousands for a hub row -- so rows with more than PART_INLINE_TUPLES are
+// queued in shared memory and written by the whole block together instead of by their one thread.
+constexpr int PART_INLINE_TUPLES = 8;
+constexpr int PART_HEAVY_QUEUE = 128;
+
 __global__ void __launch_bounds__(PART_BLOCK)
 part_emit_kernel(const int *__restrict__ indptr, int64_t n_rows, const int *__restrict__ tile_incoming_head,
                  const int64_t *__restrict__ tile_offset, int4 *__restrict__ block4)
 {
     __shared__ int s_ip[PART_SMEM_INTS];
     __shared__ int s_scan[PART_BLOCK / 32 + 1];
-    const PartTile t = part_load_tile(indptr, n_rows, s_ip);
+    __shared__ int s_heavy_n;
+    __shared__ int s_heavy_row[PART_HEAVY_QUEUE], s_heavy_deg[PART_HEAVY_QUEUE], s_heavy_loc[PART_HEAVY_QUEUE];
+    __shared__ int64_t s_heavy_out[PART_HEAVY_QUEUE];
+    if (threadIdx.x == 0) s_heavy_n = 0;
+    const PartTile t = part_load_tile(indptr, n_rows, s_ip);      // synchronises the block
     int cnt[PART_ITEMS];
     part_row_counts(t, tile_incoming_head[blockIdx.x], s_scan, cnt);
     int sum = 0;
@@ -184,12 +193,30 @@ part_emit_kernel(const int *__restrict__ indptr, int64_t n_rows, const int *__re
             block4[out] = make_int4(d, (int)i, loc, (part_warp_nz(d) << 16) + j);
             out += 1;
         } else {
-            for (int c = 0; c < cnt[k]; c++) {
-                const int done = c * PART_DEG_BOUND;
-                const int take = d - done < PART_DEG_BOUND ? d - done : PART_DEG_BOUND;
-                block4[out + c] = make_int4(d, (int)i, loc + done, take);
+            int slot = PART_HEAVY_QUEUE;
+            if (cnt[k] > PART_INLINE_TUPLES) slot = atomicAdd(&s_heavy_n, 1);
+            if (slot < PART_HEAVY_QUEUE) {
+                s_heavy_row[slot] = (int)i; s_heavy_deg[slot] = d; s_heavy_loc[slot] = loc; s_heavy_out[slot] = out;
+            } else {
+                for (int c = 0; c < cnt[k]; c++) {
+                    const int done = c * PART_DEG_BOUND;
+                    const int take = d - done < PART_DEG_BOUND ? d - done : PART_DEG_BOUND;
+                    block4[out + c] = make_int4(d, (int)i, loc + done, take);
+                }
             }
             out += cnt[k];
+        }
+    }
+    __syncthreads();
+    const int n_heavy = s_heavy_n < PART_HEAVY_QUEUE ? s_heavy_n : PART_HEAVY_QUEUE;
+    for (int q = 0; q < n_heavy; q++) {
+        const int d = s_heavy_deg[q], row = s_heavy_row[q], loc = s_heavy_loc[q];
+        const int64_t o = s_heavy_out[q];
+        const int n_tuples = (d + PART_DEG_BOUND - 1) / PART_DEG_BOUND;
+        for (int c = threadIdx.x; c < n_tuples; c += PART_BLOCK) {
+            const int done = c * PART_DEG_BOUND;
+            const int take = d - done < PART_DEG_BOUND ? d - done : PART_DEG_BOUND;
+            block4[o + c] = make_int4(d, row, loc + done, take);
         }
     }
 }
