@@ -260,10 +260,19 @@ def ours(args, rank, world, local_rank):
     torch.cuda.empty_cache()
 
     def step(record=None):
+        # the products of a step are independent: all their all-gathers are started first (they run
+        # on the process group's stream), and each SpMM waits only for its own operand
+        pending = [shard.gather_async(xs[d]) for d in dims] if world > 1 else None
         for di, d in enumerate(dims):
             if record is not None:
                 record[di][0].record()
-            shard.step(xs[d], ys[d])
+            if pending is None:
+                shard.step(xs[d], ys[d])
+            else:
+                x_full, work = pending[di]
+                if work is not None:
+                    work.wait()
+                shard.step(None, ys[d], x_gathered=x_full)
             if record is not None:
                 record[di][1].record()
 

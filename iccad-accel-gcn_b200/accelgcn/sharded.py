@@ -41,7 +41,7 @@ def shard_rows(indptr, indices, vals, cuts, rank: int):
     return indptr[r0:r1 + 1] - indptr[r0], indices[p0:p1], vals[p0:p1]
 
 
-def all_gather_rows(x_local, cuts, rank: int, world_size: int, out=None, group=None):
+def all_gather_rows(x_local, cuts, rank: int, world_size: int, out=None, group=None, async_op: bool = False):
     """All-gather row blocks of different heights: rank r contributes rows [cuts[r], cuts[r+1]) of
     the [n x dim] result.  On NCCL this is one all-gather call with per-rank sizes (grouped
     broadcasts inside the library); on other backends (the gloo CPU tests) one broadcast per rank."""
@@ -55,13 +55,14 @@ def all_gather_rows(x_local, cuts, rank: int, world_size: int, out=None, group=N
         return out
     blocks = [out[int(cuts[r]):int(cuts[r + 1])] for r in range(world_size)]
     if dist.get_backend(group) == "nccl":
-        dist.all_gather(blocks, x_local.contiguous(), group=group)
+        work = dist.all_gather(blocks, x_local.contiguous(), group=group, async_op=async_op)
+        return (out, work) if async_op else out
     else:
         blocks[rank].copy_(x_local)
         for r in range(world_size):
             if blocks[r].numel():
                 dist.broadcast(blocks[r], src=dist.get_global_rank(group, r) if group is not None else r, group=group)
-    return out
+    return (out, None) if async_op else out
 
 
 class ShardedSpmm:
@@ -92,6 +93,20 @@ class ShardedSpmm:
     @property
     def row_range(self):
         return int(self.cuts[self.rank]), int(self.cuts[self.rank + 1])
+
+    def gather_async(self, x_local):
+        """Start the all-gather of this rank's rows of the dense operand and return (buffer, work).
+        The collective runs on the process group's own stream; call work.wait() (it only makes the
+        current stream wait) before multiplying.  Gathers of independent operands can therefore be
+        in flight while earlier products are still being computed.  One buffer per width."""
+        dim = x_local.shape[1]
+        if self.world == 1:
+            return x_local, None
+        buf = self._gather.get(dim)
+        if buf is None:
+            buf = self._torch.empty((self.n_cols, dim), dtype=x_local.dtype, device=self.device)
+            self._gather[dim] = buf
+        return all_gather_rows(x_local, self.cuts, self.rank, self.world, out=buf, group=self.group, async_op=True)
 
     def step(self, x_local, y_local, x_gathered=None):
         """y_local[n_local x dim] = A_shard @ allgather(x_local).  Asynchronous on the current stream.
