@@ -110,6 +110,11 @@ def test_two_layer_gcn_forward_matches_fp64(world):
     if world == 1:
         from accelgcn import gcn
         fwd = gcn.GcnForward(shards[0], [w1, w2])
+        assert fwd.panel_cols is None
         assert torch.equal(fwd.forward(x).cpu(), torch.from_numpy(out))
+        # the column-panelled schedule used across GPUs (exchange and multiply 32 columns at a time)
+        paneled = gcn.GcnForward(shards[0], [w1, w2], panel_cols=32).forward(x).cpu().numpy()
+        assert np.all(np.abs(paneled - ref) <= 4e-3 * scale)
+        assert np.all(np.abs(paneled - out) <= 1e-5 + 1e-4 * np.abs(out))
     for sh in shards:
         sh.close()
