@@ -253,35 +253,35 @@ def ours(args, rank, world, local_rank):
     if world > 1:
         dist.all_reduce(nb)
     n_blocks = int(nb.item())
-    xs = {d: synth.features(n, d, g.info["seed"], dev)[r0:r1].contiguous() for d in dims}
+    # the dense operand is block-distributed evenly over the ranks (one balanced all-gather per
+    # product); on one GPU the block is the whole operand
+    xs = {d: shard.even_block(synth.features(n, d, g.info["seed"], dev)) for d in dims}
     ys = {d: torch.empty((r1 - r0, d), dtype=torch.float32, device=dev) for d in dims}
     if world > 1:
         del ip, ix, v
     torch.cuda.empty_cache()
 
+    launches = [0]
+
     def step(record=None):
         # the products of a step are independent: all their all-gathers are started first (they run
         # on the process group's stream), and each SpMM waits only for its own operand
-        pending = [shard.gather_async(xs[d]) for d in dims] if world > 1 else None
+        pending = [shard.gather_even_async(xs[d]) for d in dims]
+        launches[0] = 0
         for di, d in enumerate(dims):
             if record is not None:
                 record[di][0].record()
-            if pending is None:
-                shard.step(xs[d], ys[d])
-            else:
-                x_full, work = pending[di]
-                if work is not None:
-                    work.wait()
-                shard.step(None, ys[d], x_gathered=x_full)
+            x_full, work = pending[di]
+            if work is not None:
+                work.wait()
+            shard.step(None, ys[d], x_gathered=x_full)
+            launches[0] += shard.plan.info()["launches_last_run"]
             if record is not None:
                 record[di][1].record()
 
     for _ in range(max(args.warmup, 3)):
         step()
-    launches_per_step = 0
-    for d in dims:
-        shard.step(xs[d], ys[d])
-        launches_per_step += shard.plan.info()["launches_last_run"]
+    launches_per_step = launches[0]
     barrier()
 
     uuid = str(getattr(torch.cuda.get_device_properties(dev), "uuid", ""))

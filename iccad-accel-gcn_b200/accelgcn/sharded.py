@@ -65,6 +65,27 @@ def all_gather_rows(x_local, cuts, rank: int, world_size: int, out=None, group=N
     return (out, None) if async_op else out
 
 
+def even_rows(n: int, world_size: int) -> int:
+    """Rows per rank when the dense operand is block-distributed evenly (the last block is padded)."""
+    return -(-int(n) // int(world_size))
+
+
+def all_gather_even(x_block, world_size: int, out=None, group=None, async_op: bool = False):
+    """All-gather of equal blocks [rows_per_rank x dim] into [world_size * rows_per_rank x dim]:
+    one balanced collective (every rank sends the same amount), for a dense operand whose rows are
+    distributed evenly rather than along the nnz-balanced cuts of A."""
+    import torch
+    import torch.distributed as dist
+    per, dim = x_block.shape
+    if out is None:
+        out = torch.empty((world_size * per, dim), dtype=x_block.dtype, device=x_block.device)
+    if world_size == 1:
+        out.copy_(x_block)
+        return (out, None) if async_op else out
+    work = dist.all_gather_into_tensor(out, x_block.contiguous(), group=group, async_op=async_op)
+    return (out, work) if async_op else out
+
+
 class ShardedSpmm:
     """This rank's shard of a degree-ordered A, ready to multiply.
 
@@ -93,6 +114,32 @@ class ShardedSpmm:
     @property
     def row_range(self):
         return int(self.cuts[self.rank]), int(self.cuts[self.rank + 1])
+
+    def even_block(self, x_full_rows):
+        """This rank's block of an evenly distributed dense operand, given a callable or tensor that
+        yields rows [a, b) of it; the last rank's block is zero-padded to the common height."""
+        per = even_rows(self.n, self.world)
+        a, b = min(self.n, self.rank * per), min(self.n, (self.rank + 1) * per)
+        rows = x_full_rows(a, b) if callable(x_full_rows) else x_full_rows[a:b]
+        if rows.shape[0] == per:
+            return rows.contiguous()
+        blk = self._torch.zeros((per, rows.shape[1]), dtype=rows.dtype, device=rows.device)
+        blk[: rows.shape[0]] = rows
+        return blk
+
+    def gather_even_async(self, x_block):
+        """Start the balanced all-gather of an evenly distributed operand (see all_gather_even);
+        returns (buffer, work).  Column ids index the buffer directly: block r starts at row
+        r * rows_per_rank = the global row id of its first row."""
+        dim = x_block.shape[1]
+        if self.world == 1:
+            return x_block, None
+        key = ("even", dim)
+        buf = self._gather.get(key)
+        if buf is None:
+            buf = self._torch.empty((self.world * x_block.shape[0], dim), dtype=x_block.dtype, device=self.device)
+            self._gather[key] = buf
+        return all_gather_even(x_block, self.world, out=buf, group=self.group, async_op=True)
 
     def gather_async(self, x_local):
         """Start the all-gather of this rank's rows of the dense operand and return (buffer, work).

@@ -61,6 +61,13 @@ def _worker(rank, world, port, dim, result_dir):
         r0, r1 = int(cuts[rank]), int(cuts[rank + 1])
         x_full = sharded.all_gather_rows(torch.from_numpy(x[r0:r1].copy()), cuts, rank, world).numpy()
         assert np.array_equal(x_full, x)          # uneven blocks land in global row order
+        # the evenly distributed operand: one balanced all-gather, rows in global order, tail padded
+        per = sharded.even_rows(n, world)
+        blk = np.zeros((per, dim), dtype=np.float32)
+        a, b = min(n, rank * per), min(n, (rank + 1) * per)
+        blk[: b - a] = x[a:b]
+        x_even = sharded.all_gather_even(torch.from_numpy(blk), world).numpy()
+        assert x_even.shape[0] == world * per and np.array_equal(x_even[:n], x)
         # the shard's own .block4 and product, computed by the oracle (this is a CPU test)
         y = oracle.spmm_block4(oracle.partition(ip), ix, v, x_full, r1 - r0)
         np.save(os.path.join(result_dir, f"y{rank}.npy"), y)
