@@ -49,6 +49,10 @@ WORKLOADS = {
     "cfg5-small": (5, 0.002, (128,)),
 }
 GCN_WORKLOADS = ("cfg5", "cfg5-5m", "cfg5-1m", "cfg5-small")
+# "replicas": the 16 graphs of the reference's benchmark set whose .block4 files it ships, rebuilt
+# from the degree sequence each file inverts to (tests/golden/block4_kat.json) with seeded uniform
+# random column ids -- the real edge lists are a download that is not available offline
+WORKLOADS["replicas"] = (0, 1.0, (64,))
 METRIC, UNIT = "spmm_gflops", "GFLOP/s"
 FALLBACK_HBM_GBS = 6650.0
 NCU_TRAFFIC_BYTES = {("cfg2", 128): 4.070e9}      # (workload, dim) -> DRAM bytes per product, from ncu
@@ -564,6 +568,75 @@ def ours_gcn(args, rank, world, local_rank):
     print(json.dumps(line), flush=True)
 
 
+def ours_replicas(args):
+    """SpMM on degree-sequence replicas of the reference's own benchmark graphs, one width, beside the
+    reference's kernel and its cuSPARSE call on the same arrays.  Also re-checks that the GPU
+    partitioner reproduces every golden .block4 file (SHA-256) on the way."""
+    import hashlib
+    import torch
+    from accelgcn import synth, partition, spmm as spmm_mod, _lib
+    from oracle import oracle
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device: the library has no CPU fallback"
+    _lib.load()
+    dev = torch.device("cuda", 0)
+    dim = args.dim
+    with open(os.path.join(ROOT, "tests", "golden", "block4_kat.json")) as fh:
+        kat = json.load(fh)
+    rows, tot_flops, tot_ms, launches = [], 0.0, 0.0, 0
+    for gi, (name, e) in enumerate(sorted(kat.items())):
+        deg = np.concatenate([np.zeros(e["leading_zero_rows"], dtype=np.int64),
+                              np.repeat(np.asarray(e["degrees"], dtype=np.int64), np.asarray(e["counts"], dtype=np.int64))])
+        n, nnz = len(deg), int(deg.sum())
+        ip_h = np.concatenate([[0], np.cumsum(deg)]).astype(np.int32)
+        ip = torch.from_numpy(ip_h).to(dev)
+        ix = synth.uniform_int(2000 + gi, 1, 0, nnz, n, dev).to(torch.int32)
+        v = 1.0 - synth.uniform_f32(2000 + gi, 2, 0, nnz, 0.0, 1.0, dev)
+        x = synth.features(n, dim, 2000 + gi, dev)
+        b4 = partition.block_level_partition_device(ip)
+        golden = hashlib.sha256(b4.cpu().numpy().tobytes()).hexdigest() == e["sha256"]
+        plan = spmm_mod.SpmmPlan(b4, ix, n, n)
+        y = torch.empty((n, dim), dtype=torch.float32, device=dev)
+        for _ in range(max(args.warmup, 3)):
+            plan.run(ix, v, x, y)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            plan.run(ix, v, x, y)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / args.steps
+        launches += args.steps * plan.info()["launches_last_run"]
+        plan.close()
+        row = {"graph": name, "n": n, "nnz": nnz, "n_blocks": int(b4.shape[0]), "block4_matches_golden": golden,
+               "ms": ms, "gflops": 2.0 * nnz * dim / ms / 1e6,
+               "hbm_frac": min_bytes(nnz, int(b4.shape[0]), n, n, dim) / ms / 1e6 / hbm_peak()[0]}
+        if oracle.ref_available() and not args.no_ref_gpu and n * dim < 2**31:
+            ix_h, v_h, x_h, b4_h = ix.cpu().numpy(), v.cpu().numpy(), x.cpu().numpy(), b4.cpu().numpy()
+            ref = oracle.ref_accel_spmm(b4_h, ip_h, ix_h, v_h, x_h)
+            err = np.abs(y.cpu().numpy() - ref)
+            row["max_abs_diff_vs_reference_kernel"] = float(err.max())
+            row["accel_ms"] = oracle.ref_accel_spmm(b4_h, ip_h, ix_h, v_h, x_h, timing=True) * 1e3
+            row["cusparse_ms"] = oracle.ref_cusparse_spmm(ip_h, ix_h, v_h, x_h, timing=True) * 1e3
+        rows.append(row)
+        tot_flops += 2.0 * nnz * dim
+        tot_ms += ms
+        del ip, ix, v, x, y, b4
+        torch.cuda.empty_cache()
+    line = {"metric": METRIC, "value": tot_flops / tot_ms / 1e6, "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": tot_ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"replicas: degree-sequence replicas of the 16 reference graphs with shipped .block4 files, "
+                                   f"uniform random columns, SpMM at dim {dim}; one step = all 16 graphs",
+                       "dim": dim, "l2": "small graphs fit L2; no flush (the reference's protocol does not flush either)"},
+            "graphs": rows, "gpu_launches": launches}
+    have = [r for r in rows if "accel_ms" in r]
+    if have:
+        line["geomean_speedup_vs_reference_kernel"] = float(np.exp(np.mean([np.log(r["accel_ms"] / r["ms"]) for r in have])))
+        line["geomean_speedup_vs_cusparse"] = float(np.exp(np.mean([np.log(r["cusparse_ms"] / r["ms"]) for r in have])))
+    print(json.dumps(line), flush=True)
+
+
 def reference_gpu_kernels(block4, ip_h, ix_h, v_h, xs_h, dims, nnz):
     """The reference's own spmm_accel kernel and its cuSPARSE call, compiled from the reference
     sources (oracle/_ref), timed on this GPU with the reference's own protocol (mean wall-clock
@@ -592,13 +665,20 @@ def main():
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="cfg2")
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="CPU time spent on the cpu_baseline sample")
     ap.add_argument("--no-ref-gpu", action="store_true", help="skip timing the reference's GPU kernels")
+    ap.add_argument("--dim", type=int, default=64, help="dense width of the replicas workload")
     ap.add_argument("--kernel-only", action="store_true", help="resident-data loop only (for profiling under ncu)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if args.impl == "reference":
+    if args.impl == "reference" and args.workload == "replicas":
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": "the replicas workload has no CPU arm; use a cfg workload"}))
+    elif args.impl == "reference":
         reference_arm(args, rank, world)
+    elif args.workload == "replicas":
+        if rank == 0:
+            ours_replicas(args)
     elif args.workload in GCN_WORKLOADS:
         ours_gcn(args, rank, world, local_rank)
     else:

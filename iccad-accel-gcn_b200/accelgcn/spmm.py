@@ -28,6 +28,7 @@ class SpmmPlan:
         self._lib = lib
         self.block4 = block4            # keep alive: the plan borrows it
         self.device = block4.device
+        self._dev_index = block4.device.index if block4.device.index is not None else torch.cuda.current_device()
         self.n_rows, self.n_cols = int(n_rows), int(n_cols)
         self.n_blocks = block4.numel() // 4
         self.nnz = int(indices.numel())
@@ -45,9 +46,15 @@ class SpmmPlan:
         ldx = int(x.stride(0) if ldx is None and x.dim() == 2 else (dim if ldx is None else ldx))
         ldy = int(y.stride(0) if ldy is None and y.dim() == 2 else (dim if ldy is None else ldy))
         s = stream if stream is not None else torch.cuda.current_stream(self.device)
-        with torch.cuda.device(self.device):
-            _lib.check(self._lib.agcn_spmm_run_act(self._h, indices.data_ptr(), vals.data_ptr(), x.data_ptr(), ldx,
-                                                   y.data_ptr(), ldy, dim, 1 if relu else 0, s.cuda_stream))
+        args = (self._h, indices.data_ptr(), vals.data_ptr(), x.data_ptr(), ldx, y.data_ptr(), ldy, dim,
+                1 if relu else 0, s.cuda_stream)
+        if torch.cuda.current_device() == self._dev_index:      # the usual case: no device switch needed
+            rc = self._lib.agcn_spmm_run_act(*args)
+        else:
+            with torch.cuda.device(self.device):
+                rc = self._lib.agcn_spmm_run_act(*args)
+        if rc != 0:
+            _lib.check(rc)
 
     def info(self) -> dict:
         a, b, c, d = ctypes.c_int64(), ctypes.c_int64(), ctypes.c_int64(), ctypes.c_int()

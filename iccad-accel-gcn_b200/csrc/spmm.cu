@@ -15,9 +15,17 @@ struct agcn_spmm_plan {
     int *zero_rows = nullptr;         // [n_zero]
     int64_t n_carry = 0, n_zero = 0;
     int launches_last_run = 0;
+    int l2_bytes = 0;                 // of the device the plan was created on
+    int panel_override = 0;           // AGCN_SPMM_PANEL at creation (0 = choose automatically)
 };
 
 namespace agcn {
+
+static int env_int(const char *name, int dflt)
+{
+    const char *v = getenv(name);
+    return v != nullptr && *v ? atoi(v) : dflt;
+}
 
 static void plan_free(agcn_spmm_plan *p)
 {
@@ -109,6 +117,12 @@ static int spmm_create(agcn_spmm_plan **out, const int *d_block4, int64_t n_bloc
         plan_free(p);
         return AGCN_ERR_CUDA;
     }
+    {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&p->l2_bytes, cudaDevAttrL2CacheSize, dev);
+        p->panel_override = env_int("AGCN_SPMM_PANEL", 0);
+    }
     *out = p;
     return AGCN_OK;
 }
@@ -120,11 +134,7 @@ static void launch_units(const SpmmParams &prm, unsigned grid, cudaStream_t s)
     AGCN_KERNEL(k, grid, SPMM_THREADS, s, prm);
 }
 
-static int env_int(const char *name, int dflt)
-{
-    const char *v = getenv(name);
-    return v != nullptr && *v ? atoi(v) : dflt;
-}
+
 
 static int spmm_run(agcn_spmm_plan *p, const int *d_indices, const float *d_vals, const float *d_x, int64_t ldx,
                     float *d_y, int64_t ldy, int dim, cudaStream_t s, int activation = 0)
@@ -147,17 +157,14 @@ static int spmm_run(agcn_spmm_plan *p, const int *d_indices, const float *d_vals
     // When X is many times larger than L2 neither pass fits and one pass is as fast or faster
     // (6.3 against 6.5 ms at N = 5 000 000), so the split is limited to operands up to 4x L2.
     // Passes stay multiples of 32 columns so that every row segment is whole 128-byte lines.
-    // AGCN_SPMM_PANEL overrides the choice.
+    // AGCN_SPMM_PANEL (read when the plan is created) overrides the choice.
     int panel = SPMM_PANEL;
     if (dim > 64 && dim % 32 == 0 && ldx % 32 == 0) {
-        int dev = 0, l2_bytes = 0;
-        AGCN_CUDA(cudaGetDevice(&dev));
-        AGCN_CUDA(cudaDeviceGetAttribute(&l2_bytes, cudaDevAttrL2CacheSize, dev));
         const int full = dim < SPMM_PANEL ? dim : SPMM_PANEL;
         const double x_bytes = (double)p->n_cols * full * 4.0;
-        if (x_bytes > 0.75 * (double)l2_bytes && x_bytes <= 4.0 * (double)l2_bytes) panel = 64;
+        if (x_bytes > 0.75 * (double)p->l2_bytes && x_bytes <= 4.0 * (double)p->l2_bytes) panel = 64;
     }
-    panel = env_int("AGCN_SPMM_PANEL", panel);
+    if (p->panel_override > 0) panel = p->panel_override;
     AGCN_REQUIRE(panel >= 1 && panel <= SPMM_PANEL, "agcn_spmm_run: AGCN_SPMM_PANEL must be 1..%d", SPMM_PANEL);
     for (int col0 = 0; col0 < dim; col0 += panel) {
         const int width = dim - col0 < panel ? dim - col0 : panel;

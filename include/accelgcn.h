@@ -132,7 +132,7 @@ int agcn_degree_sort_host(const int32_t *h_indptr, const int32_t *h_indices, con
  * run to run.  Any dim >= 1; the fast path needs dim % 4 == 0, ldx % 4 ==
  * ldy % 4 == 0 and 16-byte aligned d_x / d_y.  dim > 64 may run as two
  * 64-column passes when X is larger than L2 (environment variable
- * AGCN_SPMM_PANEL = columns per pass overrides that choice).  A plan must not be run
+ * AGCN_SPMM_PANEL = columns per pass, read at plan creation, overrides that choice).  A plan must not be run
  * concurrently on two streams (the runs share its carry scratch).
  * ---------------------------------------------------------------------- */
 typedef struct agcn_spmm_plan agcn_spmm_plan;
