@@ -38,6 +38,10 @@ constexpr int SPMM_ZERO_ROWS_PER_BLOCK = 64;
 // and 2 x 6 / 2 x 7 by up to 30 % -- the gather wants occupancy more than per-warp depth.
 constexpr int SPMM_GATHER_BATCH = 4;
 constexpr int SPMM_MIN_BLOCKS = 5;
+// Small launches (a few thread blocks per SM at most) cannot hide latency with occupancy: there each
+// warp walks its tuple alone, so the variant used for them trades registers for a deeper batch.
+constexpr int SPMM_SMALL_GATHER_BATCH = 16;
+constexpr int SPMM_SMALL_MIN_BLOCKS = 2;
 
 struct SpmmParams {
     const int4 *block4;
@@ -186,8 +190,8 @@ __device__ __forceinline__ void gather_scalar(const int2 *pairs, int count, cons
 // dim % 4 == 0, dim <= 4*S and 16-byte aligned rows); S = 0 is the scalar
 // mode for every other dim (lane l owns columns l, l+32, l+64, l+96).
 // ---------------------------------------------------------------------------
-template <int S>
-__global__ void __launch_bounds__(SPMM_THREADS, SPMM_MIN_BLOCKS)
+template <int S, int BATCH, int MIN_BLOCKS>
+__global__ void __launch_bounds__(SPMM_THREADS, MIN_BLOCKS)
 spmm_units_kernel(const SpmmParams p)
 {
     __shared__ int2 s_pair[SPMM_WARPS][SPMM_DEG_BOUND];
@@ -241,13 +245,13 @@ spmm_units_kernel(const SpmmParams p)
         if (t.small && NS > 1 && t.row_nz <= 32) {
             // one slot per row
             for (int r = slot; r < t.n_rows; r += NS) {
-                const float4 acc = gather_vec4<SPMM_GATHER_BATCH>(pairs + r * t.row_nz, t.row_nz, 0, 1, xc, p.ldx, active, pol.keep);
+                const float4 acc = gather_vec4<BATCH>(pairs + r * t.row_nz, t.row_nz, 0, 1, xc, p.ldx, active, pol.keep);
                 if (active) st_y4(p.y + (int64_t)(t.row0 + r) * p.ldy + col, relu4(acc, p.relu), pol.stream);
             }
         } else {
             // the slots of the warp share each row
             for (int r = 0; r < t.n_rows; r++) {
-                float4 acc = gather_vec4<SPMM_GATHER_BATCH>(pairs + r * t.row_nz, t.row_nz, slot, NS, xc, p.ldx, active, pol.keep);
+                float4 acc = gather_vec4<BATCH>(pairs + r * t.row_nz, t.row_nz, slot, NS, xc, p.ldx, active, pol.keep);
 #pragma unroll
                 for (int off = LANES; off < 32; off <<= 1) {
                     acc.x += __shfl_xor_sync(FULL_MASK, acc.x, off);

@@ -15,7 +15,7 @@ struct agcn_spmm_plan {
     int *zero_rows = nullptr;         // [n_zero]
     int64_t n_carry = 0, n_zero = 0;
     int launches_last_run = 0;
-    int l2_bytes = 0;                 // of the device the plan was created on
+    int l2_bytes = 0, sm_count = 0;   // of the device the plan was created on
     int panel_override = 0;           // AGCN_SPMM_PANEL at creation (0 = choose automatically)
 };
 
@@ -121,6 +121,7 @@ static int spmm_create(agcn_spmm_plan **out, const int *d_block4, int64_t n_bloc
         int dev = 0;
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&p->l2_bytes, cudaDevAttrL2CacheSize, dev);
+        cudaDeviceGetAttribute(&p->sm_count, cudaDevAttrMultiProcessorCount, dev);
         p->panel_override = env_int("AGCN_SPMM_PANEL", 0);
     }
     *out = p;
@@ -128,10 +129,15 @@ static int spmm_create(agcn_spmm_plan **out, const int *d_block4, int64_t n_bloc
 }
 
 template <int S>
-static void launch_units(const SpmmParams &prm, unsigned grid, cudaStream_t s)
+static void launch_units(const SpmmParams &prm, unsigned grid, bool small_launch, cudaStream_t s)
 {
-    auto k = spmm_units_kernel<S>;
-    AGCN_KERNEL(k, grid, SPMM_THREADS, s, prm);
+    if (small_launch) {
+        auto k = spmm_units_kernel<S, SPMM_SMALL_GATHER_BATCH, SPMM_SMALL_MIN_BLOCKS>;
+        AGCN_KERNEL(k, grid, SPMM_THREADS, s, prm);
+    } else {
+        auto k = spmm_units_kernel<S, SPMM_GATHER_BATCH, SPMM_MIN_BLOCKS>;
+        AGCN_KERNEL(k, grid, SPMM_THREADS, s, prm);
+    }
 }
 
 
@@ -149,6 +155,7 @@ static int spmm_run(agcn_spmm_plan *p, const int *d_indices, const float *d_vals
     const int64_t zero_blocks = ceil_div(p->n_zero, SPMM_ZERO_ROWS_PER_BLOCK);
     const int64_t grid = p->n_units + zero_blocks;
     AGCN_REQUIRE(grid < (int64_t)INT32_MAX, "agcn_spmm_run: grid too large");
+    const bool small_launch = p->n_units <= (int64_t)SPMM_SMALL_MIN_BLOCKS * p->sm_count;
     // Column panels.  The gather re-reads a row of X once per nonzero of that column, so it runs
     // at L2 speed only while the X columns of a pass stay L2-resident.  When dim > 64 and the
     // operand is somewhat larger than what L2 keeps, two 64-column passes (each re-streaming the
@@ -179,11 +186,11 @@ static int spmm_run(agcn_spmm_plan *p, const int *d_indices, const float *d_vals
         prm.relu = activation;
         const bool vec = width % 4 == 0 && ldx % 4 == 0 && ldy % 4 == 0 && aligned16(prm.x) && aligned16(prm.y);
         if (grid > 0) {
-            if (!vec) launch_units<0>(prm, (unsigned)grid, s);
-            else if (width <= 16) launch_units<4>(prm, (unsigned)grid, s);
-            else if (width <= 32) launch_units<8>(prm, (unsigned)grid, s);
-            else if (width <= 64) launch_units<16>(prm, (unsigned)grid, s);
-            else launch_units<32>(prm, (unsigned)grid, s);
+            if (!vec) launch_units<0>(prm, (unsigned)grid, small_launch, s);
+            else if (width <= 16) launch_units<4>(prm, (unsigned)grid, small_launch, s);
+            else if (width <= 32) launch_units<8>(prm, (unsigned)grid, small_launch, s);
+            else if (width <= 64) launch_units<16>(prm, (unsigned)grid, small_launch, s);
+            else launch_units<32>(prm, (unsigned)grid, small_launch, s);
             AGCN_LAUNCH_CHECK("spmm_units_kernel");
             p->launches_last_run++;
         }
