@@ -311,3 +311,36 @@ def test_single_heavy_row_spanning_many_units():
                   torch.from_numpy(x).to(dev), 1).cpu().numpy()
     ref = oracle.spmm_csr(indptr, idx, val, x)
     assert spmm_close(y, ref, row_abs_scale(indptr, val, x)).all()
+
+
+def test_full_size_config2_checksum_and_sampled_rows():
+    # the headline workload at its full size (250 000 nodes, ~1.2e8 nonzeros): properties that need
+    # no full oracle -- 1^T (A X) = (1^T A) X in fp64, a row sample against the fp64 product, and
+    # bit-identical output from two runs
+    import torch
+    from accelgcn import synth, degree_sort, partition, spmm
+    dev = require_cuda()
+    g = synth.make_config(2, dev, 1.0)
+    _, ip, ix, v = degree_sort.degree_sort_device(g.indptr, g.indices, g.vals, relabel_cols=True)
+    b4 = partition.block_level_partition_device(ip)
+    n, dim = g.n, 64
+    x = synth.features(n, dim, 1002, dev)
+    plan = spmm.SpmmPlan(b4, ix, n, n)
+    y1 = torch.full((n, dim), float("nan"), device=dev)
+    y2 = torch.full((n, dim), 7.0, device=dev)
+    plan.run(ix, v, x, y1)
+    plan.run(ix, v, x, y2)
+    torch.cuda.synchronize()
+    plan.close()
+    assert torch.equal(y1, y2)
+    col_weight = torch.zeros(n, dtype=torch.float64, device=dev).index_add_(0, ix.to(torch.int64), v.to(torch.float64))
+    want = col_weight @ x.to(torch.float64)                      # (1^T A) X
+    got = y1.to(torch.float64).sum(0)
+    assert torch.allclose(got, want, rtol=1e-6, atol=1e-6 * float(col_weight.abs().sum())), (got - want).abs().max()
+    ip_h = ip.cpu().numpy()
+    rows = np.unique(np.concatenate([np.random.default_rng(0).integers(0, n, 200), [0, n - 1, n - 2]]))
+    for r in rows:
+        a, b = int(ip_h[r]), int(ip_h[r + 1])
+        ref = (v[a:b].to(torch.float64)[:, None] * x[ix[a:b].to(torch.int64)].to(torch.float64)).sum(0)
+        err = (y1[r].to(torch.float64) - ref).abs()
+        assert bool((err <= 1e-5 + 1e-4 * ref.abs()).all()), int(r)
