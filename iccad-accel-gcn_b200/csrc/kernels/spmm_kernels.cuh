@@ -29,7 +29,11 @@
 namespace agcn {
 
 constexpr int SPMM_DEG_BOUND = 384;    // format constant of .block4 (spmm_accel.cu:11)
-constexpr int SPMM_WARPS = 8;          // tuples per unit, one per warp
+// tuples per unit, one per warp (4, 6 and 12 were measured within 2 % of 8; override to experiment)
+#ifndef AGCN_SPMM_WARPS
+#define AGCN_SPMM_WARPS 8
+#endif
+constexpr int SPMM_WARPS = AGCN_SPMM_WARPS;
 constexpr int SPMM_THREADS = SPMM_WARPS * 32;
 constexpr int SPMM_PANEL = 128;        // dense columns covered by one launch
 constexpr int SPMM_ZERO_ROWS_PER_BLOCK = 64;
@@ -37,11 +41,11 @@ constexpr int SPMM_ZERO_ROWS_PER_BLOCK = 64;
 // Measured on B200: 4 in flight x 5 blocks (40 warps per SM, 48 registers) beats 8 x 3 by 10-20 %
 // and 2 x 6 / 2 x 7 by up to 30 % -- the gather wants occupancy more than per-warp depth.
 constexpr int SPMM_GATHER_BATCH = 4;
-constexpr int SPMM_MIN_BLOCKS = 5;
+constexpr int SPMM_MIN_BLOCKS = 40 / SPMM_WARPS;      // 40 resident warps per SM
 // Small launches (a few thread blocks per SM at most) cannot hide latency with occupancy: there each
 // warp walks its tuple alone, so the variant used for them trades registers for a deeper batch.
 constexpr int SPMM_SMALL_GATHER_BATCH = 16;
-constexpr int SPMM_SMALL_MIN_BLOCKS = 2;
+constexpr int SPMM_SMALL_MIN_BLOCKS = 16 / SPMM_WARPS;
 
 struct SpmmParams {
     const int4 *block4;
