@@ -84,3 +84,40 @@ def test_two_rank_gloo_sharded_product_equals_single_rank(world, tmp_path):
     ref = oracle.spmm_csr(indptr, idx, val, x)
     y = np.concatenate([np.load(tmp_path / f"y{r}.npy") for r in range(world)])
     assert y.shape == ref.shape and spmm_close(y, ref, np.full(len(ref), 50.0)).all()
+
+
+def _failing_worker(rank, world, port, result_dir):
+    # rank 1 leaves between steps (no collective of its own in flight); rank 0 must get an error from
+    # its next exchange within the process-group timeout instead of waiting forever
+    import datetime
+    import time
+    from accelgcn import sharded
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
+    cuts = np.array([0, 3, 6])
+    x = torch.ones((3, 4))
+    sharded.all_gather_rows(x, cuts, rank, world)            # step 1: everyone is here
+    if rank == 1:
+        os._exit(0)                                           # gone before step 2
+    t0 = time.time()
+    try:
+        sharded.all_gather_rows(x, cuts, rank, world)
+        outcome = "no error"
+    except Exception as e:                                    # noqa: BLE001
+        outcome = f"error after {time.time() - t0:.1f}s: {type(e).__name__}"
+    with open(os.path.join(result_dir, "outcome.txt"), "w") as fh:
+        fh.write(outcome)
+    os._exit(0)
+
+
+def test_a_rank_that_left_turns_the_next_exchange_into_an_error_not_a_hang(tmp_path):
+    ctx = mp.get_context("spawn")
+    port = _free_port()
+    procs = [ctx.Process(target=_failing_worker, args=(r, 2, port, str(tmp_path))) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(60)
+        assert not p.is_alive(), "a rank is still waiting: the exchange hung"
+    outcome = (tmp_path / "outcome.txt").read_text()
+    assert outcome.startswith("error after"), outcome
