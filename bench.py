@@ -384,8 +384,8 @@ def ours(args, rank, world, local_rank):
                         "gather_gbs_l2_inclusive": (nnz * (8 + 4 * d) + 4 * d * n + 16 * n_blocks) / ms / 1e6})
     top = max(per_dim, key=lambda r: r["ms"])
     fp32_peak = props.multi_processor_count * 128 * 2 * (clocks["sm_mhz"] or clocks["sm_max_mhz"] or 1965.0) * 1e6
-    # dram__bytes_read + dram__bytes_write of that product from the ncu capture summarised in
-    # profiles/spmm_units_kernel_cfg2.md (known for the default workload on one GPU only)
+    # dram__bytes_read + dram__bytes_write of that product, from an ncu capture of this same command
+    # (summarised under profiles/; known for the default workload on one GPU only)
     traffic = NCU_TRAFFIC_BYTES.get((args.workload, top["dim"])) if world == 1 else None
     roofline = {"bound": "hbm", "achieved": top["hbm_gbs"], "peak": peak, "unit": "GB/s",
                 "frac": top["hbm_frac"], "traffic": traffic, "kernel": f"spmm_units_kernel dim={top['dim']}",
