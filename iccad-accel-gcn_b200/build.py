@@ -9,7 +9,7 @@ import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-SOURCES = ["common.cu", "partition.cu", "degree_sort.cu", "spmm.cu", "gemm.cu"]
+SOURCES = ["common.cu", "partition.cu", "degree_sort.cu", "spmm.cu", "spmm_tiled.cu", "gemm.cu"]
 LIB = os.path.join(HERE, "lib", "libaccelgcn.so")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-shared"]

@@ -35,12 +35,20 @@ static int degree_sort_device(const int *d_indptr, const int *d_indices, const f
 
     AGCN_KERNEL(degree_keys_kernel, (unsigned)ceil_div(n_rows, 256), 256, s, d_indptr, n_rows, keys_a, rows_a, d_flags, d_flags + 1);
     AGCN_LAUNCH_CHECK("degree_keys_kernel");
-    int flags[2] = {0, 0};
+    int flags[2] = {0, 0}, ends[2] = {0, 0};
     AGCN_CUDA(cudaMemcpyAsync(flags, d_flags, sizeof(flags), cudaMemcpyDeviceToHost, s));
+    AGCN_CUDA(cudaMemcpyAsync(&ends[0], d_indptr, sizeof(int), cudaMemcpyDeviceToHost, s));
+    AGCN_CUDA(cudaMemcpyAsync(&ends[1], d_indptr + n_rows, sizeof(int), cudaMemcpyDeviceToHost, s));
     AGCN_CUDA(cudaStreamSynchronize(s));
     if (flags[1] != 0) {
         set_error("agcn_degree_sort: indptr decreases somewhere (negative degree)");
         return AGCN_ERR_RANGE;
+    }
+    // the caller's nnz sizes the grid of the CSR permute: it must be the matrix's own count
+    if (d_new_indices != nullptr && (int64_t)ends[1] - (int64_t)ends[0] != nnz) {
+        set_error("agcn_degree_sort: nnz = %lld but indptr[n_rows] - indptr[0] = %lld", (long long)nnz,
+                  (long long)ends[1] - (long long)ends[0]);
+        return AGCN_ERR_INVALID;
     }
     int bits = 0;
     while (bits < 32 && (flags[0] >> bits) != 0) bits++;
@@ -73,7 +81,7 @@ static int degree_sort_device(const int *d_indptr, const int *d_indices, const f
             AGCN_LAUNCH_CHECK("invert_perm_kernel");
         }
         AGCN_KERNEL(csr_permute_kernel, (unsigned)ceil_div(nnz, PERMUTE_TILE), PERMUTE_BLOCK, s,
-                    d_indptr, d_indices, d_vals, (const int *)rows_in, (const int *)d_new_indptr, (const int *)new_id,
+                    d_indptr, d_indices, d_new_vals != nullptr ? d_vals : (const float *)nullptr, (const int *)rows_in, (const int *)d_new_indptr, (const int *)new_id,
                     n_rows, nnz, d_new_indices, d_new_vals, d_flags + 1);
         AGCN_LAUNCH_CHECK("csr_permute_kernel");
         AGCN_CUDA(cudaMemcpyAsync(flags, d_flags, sizeof(flags), cudaMemcpyDeviceToHost, s));

@@ -185,7 +185,7 @@ csr_permute_kernel(const int *__restrict__ old_indptr, const int *__restrict__ o
                 c = new_id[c];
             }
             new_indices[p] = c;
-            if (old_vals != nullptr) new_vals[p] = old_vals[src];
+            if (new_vals != nullptr) new_vals[p] = old_vals[src];
         }
     }
 }

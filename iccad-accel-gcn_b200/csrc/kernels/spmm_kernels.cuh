@@ -63,6 +63,10 @@ struct SpmmParams {
     const int *zero_rows;     // rows no tuple covers
     int64_t n_zero_rows;
     int relu;                 // nonzero: Y = max(A * X, 0) (fused GCN activation)
+    // The fields below are read only by the general (PLAIN = false) kernel flavour.
+    int accumulate;           // nonzero: Y += A * X (later column ranges of a column-tiled product)
+    int y_vec;                // nonzero: rows of Y are 16-byte aligned and dim_store % 4 == 0
+    int dim_store;            // columns of Y written (dim rounded up to 4 is what is gathered)
 };
 
 struct TupleView {
@@ -92,6 +96,33 @@ __device__ __forceinline__ float4 relu4(const float4 &v, int on)
     return on ? make_float4(fmaxf(v.x, 0.f), fmaxf(v.y, 0.f), fmaxf(v.z, 0.f), fmaxf(v.w, 0.f)) : v;
 }
 __device__ __forceinline__ float relu1(float v, int on) { return on ? fmaxf(v, 0.f) : v; }
+
+// Writes columns col .. col+3 of one result row.  PLAIN: one 16-byte store.  Otherwise the row may
+// be unaligned or end inside the four columns (dim not a multiple of 4: element-wise stores), and
+// the product may be added to what the row holds (column-tiled products).
+template <bool PLAIN>
+__device__ __forceinline__ void emit_row4(const SpmmParams &p, float *yr, int col, float4 v, int act, uint64_t policy)
+{
+    if (PLAIN) {
+        st_y4(yr + col, relu4(v, act), policy);
+    } else if (p.y_vec) {
+        if (p.accumulate) {
+            const float4 o = *reinterpret_cast<const float4 *>(yr + col);
+            v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+        }
+        st_y4(yr + col, relu4(v, act), policy);
+    } else {
+        const float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int k = 0; k < 4; k++)
+            if (col + k < p.dim_store) st_y1(yr + col + k, relu1(p.accumulate ? e[k] + yr[col + k] : e[k], act), policy);
+    }
+}
+template <bool PLAIN>
+__device__ __forceinline__ void emit_row1(const SpmmParams &p, float *y, float v, int act, uint64_t policy)
+{
+    st_y1(y, relu1(!PLAIN && p.accumulate ? v + *y : v, act), policy);
+}
 
 __device__ __forceinline__ void fma4(float4 &acc, float a, const float4 &v)
 {
@@ -194,7 +225,7 @@ __device__ __forceinline__ void gather_scalar(const int2 *pairs, int count, cons
 // dim % 4 == 0, dim <= 4*S and 16-byte aligned rows); S = 0 is the scalar
 // mode for every other dim (lane l owns columns l, l+32, l+64, l+96).
 // ---------------------------------------------------------------------------
-template <int S, int BATCH, int MIN_BLOCKS>
+template <int S, int BATCH, int MIN_BLOCKS, bool PLAIN>
 __global__ void __launch_bounds__(SPMM_THREADS, MIN_BLOCKS)
 spmm_units_kernel(const SpmmParams p)
 {
@@ -214,14 +245,15 @@ spmm_units_kernel(const SpmmParams p)
 
     if ((int64_t)blockIdx.x >= p.n_units) {
         // zero-fill rows that no tuple covers
+        // (when accumulating, these rows keep their value and only the activation is applied)
         const int64_t zb = ((int64_t)blockIdx.x - p.n_units) * SPMM_ZERO_ROWS_PER_BLOCK;
         for (int k = w * NS + slot; k < SPMM_ZERO_ROWS_PER_BLOCK; k += SPMM_WARPS * NS) {
             if (zb + k >= p.n_zero_rows) break;
             float *yr = p.y + (int64_t)p.zero_rows[zb + k] * p.ldy;
             if (VEC) {
-                if (active) st_y4(yr + col, make_float4(0.f, 0.f, 0.f, 0.f), pol.stream);
+                if (active) emit_row4<PLAIN>(p, yr, col, make_float4(0.f, 0.f, 0.f, 0.f), p.relu, pol.stream);
             } else {
-                for (int c = lane; c < p.dim; c += 32) st_y1(yr + c, 0.f, pol.stream);
+                for (int c = lane; c < p.dim; c += 32) emit_row1<PLAIN>(p, yr + c, 0.f, p.relu, pol.stream);
             }
         }
         return;
@@ -250,7 +282,7 @@ spmm_units_kernel(const SpmmParams p)
             // one slot per row
             for (int r = slot; r < t.n_rows; r += NS) {
                 const float4 acc = gather_vec4<BATCH>(pairs + r * t.row_nz, t.row_nz, 0, 1, xc, p.ldx, active, pol.keep);
-                if (active) st_y4(p.y + (int64_t)(t.row0 + r) * p.ldy + col, relu4(acc, p.relu), pol.stream);
+                if (active) emit_row4<PLAIN>(p, p.y + (int64_t)(t.row0 + r) * p.ldy, col, acc, p.relu, pol.stream);
             }
         } else {
             // the slots of the warp share each row
@@ -264,7 +296,7 @@ spmm_units_kernel(const SpmmParams p)
                     acc.w += __shfl_xor_sync(FULL_MASK, acc.w, off);
                 }
                 if (slot == 0 && active) {
-                    if (t.small) st_y4(p.y + (int64_t)(t.row0 + r) * p.ldy + col, relu4(acc, p.relu), pol.stream);
+                    if (t.small) emit_row4<PLAIN>(p, p.y + (int64_t)(t.row0 + r) * p.ldy, col, acc, p.relu, pol.stream);
                     else *reinterpret_cast<float4 *>(&s_part[w][col]) = acc;
                 }
             }
@@ -277,7 +309,7 @@ spmm_units_kernel(const SpmmParams p)
             for (int k = 0; k < SPMM_SCALAR_COLS; k++) {
                 const int c = lane + 32 * k;
                 if (c < p.dim) {
-                    if (t.small) st_y1(p.y + (int64_t)(t.row0 + r) * p.ldy + c, relu1(acc[k], p.relu), pol.stream);
+                    if (t.small) emit_row1<PLAIN>(p, p.y + (int64_t)(t.row0 + r) * p.ldy + c, acc[k], p.relu, pol.stream);
                     else s_part[w][c] = acc[k];
                 }
             }
@@ -306,13 +338,15 @@ spmm_units_kernel(const SpmmParams p)
                 const float4 v = *reinterpret_cast<const float4 *>(&s_part[ww][col]);
                 sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
             }
-            *reinterpret_cast<float4 *>(dst + col) = relu4(sum, act);
+            if (partial) *reinterpret_cast<float4 *>(dst + col) = sum;      // carry slots are aligned and private
+            else emit_row4<PLAIN>(p, dst, col, sum, act, pol.stream);
         }
     } else {
         for (int c = lane; c < p.dim; c += 32) {
             float sum = s_part[w][c];
             for (int ww = w + 1; ww < w_end; ww++) sum += s_part[ww][c];
-            dst[c] = relu1(sum, act);
+            if (partial) dst[c] = sum;
+            else emit_row1<PLAIN>(p, dst + c, sum, act, pol.stream);
         }
     }
 }
@@ -323,7 +357,7 @@ spmm_units_kernel(const SpmmParams p)
 template <bool VEC>
 __global__ void __launch_bounds__(SPMM_THREADS)
 spmm_carry_kernel(const float *__restrict__ carry, const int *__restrict__ carry_row, int64_t n_carry,
-                  float *__restrict__ y, int64_t ldy, int dim, int relu)
+                  float *y, int64_t ldy, int dim, int relu, int accumulate, int y_vec, int dim_store)
 {
     const int64_t s = (int64_t)blockIdx.x * SPMM_WARPS + warp_id();
     if (s >= n_carry) return;
@@ -340,15 +374,48 @@ spmm_carry_kernel(const float *__restrict__ carry, const int *__restrict__ carry
                 const float4 v = *reinterpret_cast<const float4 *>(carry + q * SPMM_PANEL + col);
                 sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
             }
-            *reinterpret_cast<float4 *>(y + (int64_t)row * ldy + col) = relu4(sum, relu);
+            float *yr = y + (int64_t)row * ldy;
+            if (y_vec) {
+                if (accumulate) {
+                    const float4 o = *reinterpret_cast<const float4 *>(yr + col);
+                    sum.x += o.x; sum.y += o.y; sum.z += o.z; sum.w += o.w;
+                }
+                *reinterpret_cast<float4 *>(yr + col) = relu4(sum, relu);
+            } else {
+                const float e[4] = {sum.x, sum.y, sum.z, sum.w};
+#pragma unroll
+                for (int k = 0; k < 4; k++)
+                    if (col + k < dim_store) yr[col + k] = relu1(accumulate ? e[k] + yr[col + k] : e[k], relu);
+            }
         }
     } else {
         for (int c = lane; c < dim; c += 32) {
             float sum = carry[s * SPMM_PANEL + c];
             for (int64_t q = s + 1; q < s_end; q++) sum += carry[q * SPMM_PANEL + c];
-            y[(int64_t)row * ldy + c] = relu1(sum, relu);
+            float *ye = y + (int64_t)row * ldy + c;
+            *ye = relu1(accumulate ? sum + *ye : sum, relu);
         }
     }
+}
+
+// X[n_rows x dim] with row stride ldx  ->  XP[n_rows x ldp], ldp = dim rounded up to 4, tail zero:
+// the 16-byte-aligned copy of a dense operand whose rows are not (dim % 4 != 0 or an unaligned base).
+// One thread per 16 bytes written.
+__global__ void __launch_bounds__(256)
+spmm_pad_rows_kernel(const float *__restrict__ x, int64_t ldx, int dim, float *__restrict__ xp, int ldp, int64_t n_rows)
+{
+    const int quads = ldp >> 2;
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_rows * quads) return;
+    const int64_t row = i / quads;
+    const int c = (int)(i - row * quads) * 4;
+    const float *src = x + row * ldx + c;
+    float4 v;
+    v.x = c + 0 < dim ? __ldg(src + 0) : 0.f;
+    v.y = c + 1 < dim ? __ldg(src + 1) : 0.f;
+    v.z = c + 2 < dim ? __ldg(src + 2) : 0.f;
+    v.w = c + 3 < dim ? __ldg(src + 3) : 0.f;
+    *reinterpret_cast<float4 *>(xp + row * ldp + c) = v;
 }
 
 // ---------------------------------------------------------------------------

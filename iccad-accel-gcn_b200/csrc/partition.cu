@@ -1,6 +1,7 @@
 // C-ABI entry points of the block-level partitioner
 // (replaces block_level_partition.py:38-106).
 #include "host_common.h"
+#include "internal.h"
 #include "kernels/partition_kernels.cuh"
 
 #include <cstddef>
@@ -8,8 +9,60 @@
 
 namespace agcn {
 
-static int partition_device(const int *d_indptr, int64_t n_rows, int *d_block4, int64_t cap_blocks,
-                            int64_t *n_blocks, cudaStream_t s)
+// Tile scratch of one partitioner call: one run-head index and one tuple count per PART_TILE rows,
+// the tuple total and an error word.  The regular entry point allocates it per call; the
+// allocation-free one points it at a fixed array in the library's device image.
+struct PartScratch {
+    int *tile_head;
+    int64_t *tile_count;
+    int64_t *total;
+    int *err;
+};
+
+// The pipeline both entry points run.  `who` names the entry point in error messages.
+static int partition_pipeline(const char *who, const int *d_indptr, int64_t n_rows, int *d_block4, int64_t cap_blocks,
+                              int64_t *n_blocks, const PartScratch &sc, cudaStream_t s)
+{
+    const int64_t tiles = ceil_div(n_rows, PART_TILE);
+    AGCN_CUDA(cudaMemsetAsync(sc.err, 0, sizeof(int), s));      // the one word that must start at zero
+    auto k_scan_max = single_block_scan_exclusive_kernel<int, OpMax>;
+    auto k_scan_add = single_block_scan_exclusive_kernel<int64_t, OpAdd>;
+    AGCN_KERNEL(part_run_heads_kernel, (unsigned)tiles, PART_BLOCK, s, d_indptr, n_rows, sc.tile_head, sc.err);
+    AGCN_LAUNCH_CHECK("part_run_heads_kernel");
+    AGCN_KERNEL(k_scan_max, 1, 1024, s, sc.tile_head, tiles, -1, (int *)nullptr);
+    AGCN_LAUNCH_CHECK("single_block_scan_exclusive_kernel<max>");
+    AGCN_KERNEL(part_count_kernel, (unsigned)tiles, PART_BLOCK, s, d_indptr, n_rows, (const int *)sc.tile_head, sc.tile_count);
+    AGCN_LAUNCH_CHECK("part_count_kernel");
+    AGCN_KERNEL(k_scan_add, 1, 1024, s, sc.tile_count, tiles, (int64_t)0, sc.total);
+    AGCN_LAUNCH_CHECK("single_block_scan_exclusive_kernel<add>");
+
+    int64_t total = 0;
+    int err = 0;
+    AGCN_CUDA(cudaMemcpyAsync(&total, sc.total, sizeof(total), cudaMemcpyDeviceToHost, s));
+    AGCN_CUDA(cudaMemcpyAsync(&err, sc.err, sizeof(err), cudaMemcpyDeviceToHost, s));
+    AGCN_CUDA(cudaStreamSynchronize(s));
+    if (err != 0) {
+        set_error("%s: indptr decreases somewhere (negative degree); "
+                  "the reference script prints 'cur_degree number is wrong' and stops", who);
+        return AGCN_ERR_RANGE;
+    }
+    *n_blocks = total;
+    if (d_block4 == nullptr || cap_blocks == 0) return AGCN_OK;
+    if (cap_blocks < total) {
+        set_error("%s: %lld blocks needed, capacity %lld", who, (long long)total, (long long)cap_blocks);
+        return AGCN_ERR_CAPACITY;
+    }
+    if (total > 0) {
+        AGCN_KERNEL(part_emit_kernel, (unsigned)tiles, PART_BLOCK, s, d_indptr, n_rows, (const int *)sc.tile_head,
+                    (const int64_t *)sc.tile_count, reinterpret_cast<int4 *>(d_block4));
+        AGCN_LAUNCH_CHECK("part_emit_kernel");
+    }
+    AGCN_CUDA(cudaStreamSynchronize(s));
+    return AGCN_OK;
+}
+
+int partition_device(const int *d_indptr, int64_t n_rows, int *d_block4, int64_t cap_blocks,
+                     int64_t *n_blocks, cudaStream_t s)
 {
     AGCN_REQUIRE(d_indptr != nullptr && n_blocks != nullptr, "agcn_partition: null pointer");
     AGCN_REQUIRE(n_rows > 0, "agcn_partition: empty graph (n_rows = %lld); the reference script raises IndexError here",
@@ -21,46 +74,13 @@ static int partition_device(const int *d_indptr, int64_t n_rows, int *d_block4, 
 
     const int64_t tiles = ceil_div(n_rows, PART_TILE);
     DeviceScratch scratch;
+    PartScratch sc;
     AGCN_ALLOC(tile_head, scratch, int, tiles);
     AGCN_ALLOC(tile_count, scratch, int64_t, tiles);
     AGCN_ALLOC(d_total, scratch, int64_t, 1);
     AGCN_ALLOC(d_err, scratch, int, 1);
-    AGCN_CUDA(cudaMemsetAsync(d_err, 0, sizeof(int), s));
-
-    auto k_scan_max = single_block_scan_exclusive_kernel<int, OpMax>;
-    auto k_scan_add = single_block_scan_exclusive_kernel<int64_t, OpAdd>;
-    AGCN_KERNEL(part_run_heads_kernel, (unsigned)tiles, PART_BLOCK, s, d_indptr, n_rows, tile_head, d_err);
-    AGCN_LAUNCH_CHECK("part_run_heads_kernel");
-    AGCN_KERNEL(k_scan_max, 1, 1024, s, tile_head, tiles, -1, (int *)nullptr);
-    AGCN_LAUNCH_CHECK("single_block_scan_exclusive_kernel<max>");
-    AGCN_KERNEL(part_count_kernel, (unsigned)tiles, PART_BLOCK, s, d_indptr, n_rows, (const int *)tile_head, tile_count);
-    AGCN_LAUNCH_CHECK("part_count_kernel");
-    AGCN_KERNEL(k_scan_add, 1, 1024, s, tile_count, tiles, (int64_t)0, d_total);
-    AGCN_LAUNCH_CHECK("single_block_scan_exclusive_kernel<add>");
-
-    int64_t total = 0;
-    int err = 0;
-    AGCN_CUDA(cudaMemcpyAsync(&total, d_total, sizeof(total), cudaMemcpyDeviceToHost, s));
-    AGCN_CUDA(cudaMemcpyAsync(&err, d_err, sizeof(err), cudaMemcpyDeviceToHost, s));
-    AGCN_CUDA(cudaStreamSynchronize(s));
-    if (err != 0) {
-        set_error("agcn_partition: indptr decreases somewhere (negative degree); "
-                  "the reference script prints 'cur_degree number is wrong' and stops");
-        return AGCN_ERR_RANGE;
-    }
-    *n_blocks = total;
-    if (d_block4 == nullptr || cap_blocks == 0) return AGCN_OK;
-    if (cap_blocks < total) {
-        set_error("agcn_partition: %lld blocks needed, capacity %lld", (long long)total, (long long)cap_blocks);
-        return AGCN_ERR_CAPACITY;
-    }
-    if (total > 0) {
-        AGCN_KERNEL(part_emit_kernel, (unsigned)tiles, PART_BLOCK, s, d_indptr, n_rows, (const int *)tile_head,
-                    (const int64_t *)tile_count, reinterpret_cast<int4 *>(d_block4));
-        AGCN_LAUNCH_CHECK("part_emit_kernel");
-    }
-    AGCN_CUDA(cudaStreamSynchronize(s));
-    return AGCN_OK;
+    sc.tile_head = tile_head; sc.tile_count = tile_count; sc.total = d_total; sc.err = d_err;
+    return partition_pipeline("agcn_partition", d_indptr, n_rows, d_block4, cap_blocks, n_blocks, sc, s);
 }
 
 }  // namespace agcn
@@ -170,50 +190,17 @@ static int partition_device_noalloc(const int *d_indptr, int64_t n_rows, int *d_
     AGCN_REQUIRE(d_block4 == nullptr || aligned16(d_block4), "agcn_partition_device_noalloc: block4 output must be 16-byte aligned");
     *n_blocks = 0;
 
-    PartStaticScratch *sc = nullptr;
-    int rc = part_static_scratch(&sc);
+    PartStaticScratch *st = nullptr;
+    int rc = part_static_scratch(&st);
     if (rc != AGCN_OK) return rc;
-    // sc is a device address: form member addresses by arithmetic only, never dereference it here
-    int64_t *tile_count = reinterpret_cast<int64_t *>(reinterpret_cast<unsigned char *>(sc) + offsetof(PartStaticScratch, tile_count));
-    int64_t *d_total = reinterpret_cast<int64_t *>(reinterpret_cast<unsigned char *>(sc) + offsetof(PartStaticScratch, total));
-    int *tile_head = reinterpret_cast<int *>(reinterpret_cast<unsigned char *>(sc) + offsetof(PartStaticScratch, tile_head));
-    int *d_err = reinterpret_cast<int *>(reinterpret_cast<unsigned char *>(sc) + offsetof(PartStaticScratch, err));
-
-    const int64_t tiles = ceil_div(n_rows, PART_TILE);
-    AGCN_CUDA(cudaMemsetAsync(d_err, 0, sizeof(int), s));      // the one word that must start at zero
-    auto k_scan_max = single_block_scan_exclusive_kernel<int, OpMax>;
-    auto k_scan_add = single_block_scan_exclusive_kernel<int64_t, OpAdd>;
-    AGCN_KERNEL(part_run_heads_kernel, (unsigned)tiles, PART_BLOCK, s, d_indptr, n_rows, tile_head, d_err);
-    AGCN_LAUNCH_CHECK("part_run_heads_kernel");
-    AGCN_KERNEL(k_scan_max, 1, 1024, s, tile_head, tiles, -1, (int *)nullptr);
-    AGCN_LAUNCH_CHECK("single_block_scan_exclusive_kernel<max>");
-    AGCN_KERNEL(part_count_kernel, (unsigned)tiles, PART_BLOCK, s, d_indptr, n_rows, (const int *)tile_head, tile_count);
-    AGCN_LAUNCH_CHECK("part_count_kernel");
-    AGCN_KERNEL(k_scan_add, 1, 1024, s, tile_count, tiles, (int64_t)0, d_total);
-    AGCN_LAUNCH_CHECK("single_block_scan_exclusive_kernel<add>");
-
-    int64_t total = 0;
-    int err = 0;
-    AGCN_CUDA(cudaMemcpyAsync(&total, d_total, sizeof(total), cudaMemcpyDeviceToHost, s));
-    AGCN_CUDA(cudaMemcpyAsync(&err, d_err, sizeof(err), cudaMemcpyDeviceToHost, s));
-    AGCN_CUDA(cudaStreamSynchronize(s));
-    if (err != 0) {
-        set_error("agcn_partition_device_noalloc: indptr decreases somewhere (negative degree)");
-        return AGCN_ERR_RANGE;
-    }
-    *n_blocks = total;
-    if (d_block4 == nullptr || cap_blocks == 0) return AGCN_OK;
-    if (cap_blocks < total) {
-        set_error("agcn_partition_device_noalloc: %lld blocks needed, capacity %lld", (long long)total, (long long)cap_blocks);
-        return AGCN_ERR_CAPACITY;
-    }
-    if (total > 0) {
-        AGCN_KERNEL(part_emit_kernel, (unsigned)tiles, PART_BLOCK, s, d_indptr, n_rows, (const int *)tile_head,
-                    (const int64_t *)tile_count, reinterpret_cast<int4 *>(d_block4));
-        AGCN_LAUNCH_CHECK("part_emit_kernel");
-    }
-    AGCN_CUDA(cudaStreamSynchronize(s));
-    return AGCN_OK;
+    // st is a device address: form member addresses by arithmetic only, never dereference it here
+    unsigned char *base = reinterpret_cast<unsigned char *>(st);
+    PartScratch sc;
+    sc.tile_count = reinterpret_cast<int64_t *>(base + offsetof(PartStaticScratch, tile_count));
+    sc.total = reinterpret_cast<int64_t *>(base + offsetof(PartStaticScratch, total));
+    sc.tile_head = reinterpret_cast<int *>(base + offsetof(PartStaticScratch, tile_head));
+    sc.err = reinterpret_cast<int *>(base + offsetof(PartStaticScratch, err));
+    return partition_pipeline("agcn_partition_device_noalloc", d_indptr, n_rows, d_block4, cap_blocks, n_blocks, sc, s);
 }
 
 }  // namespace agcn

@@ -1,43 +1,32 @@
 // C-ABI entry points of the SpMM plug-in (replaces SPMM_ACCEL,
 // spmm_accel.cu:104-139) and of the host-buffer call.
 #include "host_common.h"
+#include "internal.h"
 #include "kernels/spmm_kernels.cuh"
 
 #include <cstdlib>
 #include <new>
 
-struct agcn_spmm_plan {
-    const int4 *block4 = nullptr;     // borrowed
-    int64_t n_blocks = 0, n_units = 0, n_rows = 0, n_cols = 0, nnz = 0;
-    int2 *unit_carry = nullptr;       // [n_units]
-    int *carry_row = nullptr;         // [n_carry]
-    float *carry = nullptr;           // [n_carry][SPMM_PANEL]
-    int *zero_rows = nullptr;         // [n_zero]
-    int64_t n_carry = 0, n_zero = 0;
-    int launches_last_run = 0;
-    int l2_bytes = 0, sm_count = 0;   // of the device the plan was created on
-    int panel_override = 0;           // AGCN_SPMM_PANEL at creation (0 = choose automatically)
-};
-
 namespace agcn {
 
-static int env_int(const char *name, int dflt)
+int env_int(const char *name, int dflt)
 {
     const char *v = getenv(name);
     return v != nullptr && *v ? atoi(v) : dflt;
 }
 
-static void plan_free(agcn_spmm_plan *p)
+void plan_free(agcn_spmm_plan *p)
 {
     if (p == nullptr) return;
     cudaFree(p->unit_carry);
     cudaFree(p->carry_row);
     cudaFree(p->carry);
     cudaFree(p->zero_rows);
+    cudaFree(p->x_pad);
     delete p;
 }
 
-static int spmm_create(agcn_spmm_plan **out, const int *d_block4, int64_t n_blocks, const int *d_indices,
+int spmm_create(agcn_spmm_plan **out, const int *d_block4, int64_t n_blocks, const int *d_indices,
                        int64_t n_rows, int64_t n_cols, int64_t nnz, cudaStream_t s)
 {
     AGCN_REQUIRE(out != nullptr, "agcn_spmm_create: null plan pointer");
@@ -123,27 +112,70 @@ static int spmm_create(agcn_spmm_plan **out, const int *d_block4, int64_t n_bloc
         cudaDeviceGetAttribute(&p->l2_bytes, cudaDevAttrL2CacheSize, dev);
         cudaDeviceGetAttribute(&p->sm_count, cudaDevAttrMultiProcessorCount, dev);
         p->panel_override = env_int("AGCN_SPMM_PANEL", 0);
+        p->pad_unaligned = env_int("AGCN_SPMM_PAD", 1);
     }
     *out = p;
     return AGCN_OK;
 }
 
 template <int S>
-static void launch_units(const SpmmParams &prm, unsigned grid, bool small_launch, cudaStream_t s)
+static void launch_units(const SpmmParams &prm, unsigned grid, bool small_launch, bool plain, cudaStream_t s)
 {
     if (small_launch) {
-        auto k = spmm_units_kernel<S, SPMM_SMALL_GATHER_BATCH, SPMM_SMALL_MIN_BLOCKS>;
-        AGCN_KERNEL(k, grid, SPMM_THREADS, s, prm);
+        if (plain) { auto k = spmm_units_kernel<S, SPMM_SMALL_GATHER_BATCH, SPMM_SMALL_MIN_BLOCKS, true>; AGCN_KERNEL(k, grid, SPMM_THREADS, s, prm); }
+        else { auto k = spmm_units_kernel<S, SPMM_SMALL_GATHER_BATCH, SPMM_SMALL_MIN_BLOCKS, false>; AGCN_KERNEL(k, grid, SPMM_THREADS, s, prm); }
     } else {
-        auto k = spmm_units_kernel<S, SPMM_GATHER_BATCH, SPMM_MIN_BLOCKS>;
-        AGCN_KERNEL(k, grid, SPMM_THREADS, s, prm);
+        if (plain) { auto k = spmm_units_kernel<S, SPMM_GATHER_BATCH, SPMM_MIN_BLOCKS, true>; AGCN_KERNEL(k, grid, SPMM_THREADS, s, prm); }
+        else { auto k = spmm_units_kernel<S, SPMM_GATHER_BATCH, SPMM_MIN_BLOCKS, false>; AGCN_KERNEL(k, grid, SPMM_THREADS, s, prm); }
     }
 }
 
+static void launch_units_for_width(int width, bool vec, const SpmmParams &prm, unsigned grid, bool small_launch, bool plain,
+                                   cudaStream_t s)
+{
+    if (!vec) launch_units<0>(prm, grid, small_launch, plain, s);
+    else if (width <= 16) launch_units<4>(prm, grid, small_launch, plain, s);
+    else if (width <= 32) launch_units<8>(prm, grid, small_launch, plain, s);
+    else if (width <= 64) launch_units<16>(prm, grid, small_launch, plain, s);
+    else launch_units<32>(prm, grid, small_launch, plain, s);
+}
 
+// Rows of X that are not 16-byte aligned (dim % 4 != 0 with the reference's ld = dim, an odd
+// stride or base) would force 4-byte gathers: 1.2-1.6x the time of the 16-byte path.  Instead X
+// is copied once into plan-owned rows padded to a multiple of 4 floats (2 * n_cols * dim * 4
+// bytes of streaming traffic against nnz * dim * 4 bytes of gather) and the 16-byte path runs
+// on the copy; Y keeps the caller's layout and gets element-wise stores where it is unaligned.
+// On return *x_use / *ldx_use name the operand to gather from and *x_vec says whether its rows
+// are 16-byte aligned.
+int spmm_prepare_x(agcn_spmm_plan *p, const float *d_x, int64_t ldx, int dim, cudaStream_t s,
+                   const float **x_use, int64_t *ldx_use, bool *x_vec)
+{
+    const bool x_aligned = dim % 4 == 0 && ldx % 4 == 0 && aligned16(d_x);
+    *x_use = d_x;
+    *ldx_use = ldx;
+    *x_vec = x_aligned;
+    if (x_aligned || !p->pad_unaligned || p->nnz == 0) return AGCN_OK;
+    const int ldp = (dim + 3) & ~3;
+    const size_t need = (size_t)p->n_cols * ldp * sizeof(float);
+    if (need > p->x_pad_bytes) {
+        // growing the scratch synchronises the device once per plan and width; steady state allocates nothing
+        if (p->x_pad != nullptr) AGCN_CUDA(cudaFree(p->x_pad));
+        p->x_pad = nullptr; p->x_pad_bytes = 0;
+        AGCN_CUDA(cudaMalloc(&p->x_pad, need));
+        p->x_pad_bytes = need;
+    }
+    const int64_t quads = p->n_cols * (ldp >> 2);
+    AGCN_KERNEL(spmm_pad_rows_kernel, (unsigned)ceil_div(quads, 256), 256, s, d_x, ldx, dim, p->x_pad, ldp, p->n_cols);
+    AGCN_LAUNCH_CHECK("spmm_pad_rows_kernel");
+    p->launches_last_run++;
+    *x_use = p->x_pad;
+    *ldx_use = ldp;
+    *x_vec = true;
+    return AGCN_OK;
+}
 
-static int spmm_run(agcn_spmm_plan *p, const int *d_indices, const float *d_vals, const float *d_x, int64_t ldx,
-                    float *d_y, int64_t ldy, int dim, cudaStream_t s, int activation = 0)
+int spmm_check_run_args(const agcn_spmm_plan *p, const int *d_indices, const float *d_vals, const float *d_x, int64_t ldx,
+                        const float *d_y, int64_t ldy, int dim, int activation)
 {
     AGCN_REQUIRE(activation == 0 || activation == 1, "agcn_spmm_run_act: activation must be AGCN_ACT_NONE or AGCN_ACT_RELU");
     AGCN_REQUIRE(p != nullptr, "agcn_spmm_run: null plan");
@@ -151,11 +183,21 @@ static int spmm_run(agcn_spmm_plan *p, const int *d_indices, const float *d_vals
     AGCN_REQUIRE(p->nnz == 0 || (d_indices != nullptr && d_vals != nullptr), "agcn_spmm_run: null indices or values");
     AGCN_REQUIRE(dim >= 1, "agcn_spmm_run: dim = %d", dim);
     AGCN_REQUIRE(ldx >= dim && ldy >= dim, "agcn_spmm_run: row stride smaller than dim");
-    p->launches_last_run = 0;
-    const int64_t zero_blocks = ceil_div(p->n_zero, SPMM_ZERO_ROWS_PER_BLOCK);
+    return AGCN_OK;
+}
+
+// One product on one set of tuples, X already prepared.  accumulate: Y += A * X (a later column
+// range of a column-tiled product; rows no tuple covers then keep their value, and only get the
+// activation).
+int spmm_run_prepared(agcn_spmm_plan *p, const int *d_indices, const float *d_vals, const float *x_use, int64_t ldx_use,
+                      bool x_vec, float *d_y, int64_t ldy, int dim, cudaStream_t s, int activation, int accumulate)
+{
+    // rows no tuple covers: zero-filled -- or, when accumulating, left alone unless an activation is due
+    const int64_t zero_blocks = accumulate && !activation ? 0 : ceil_div(p->n_zero, SPMM_ZERO_ROWS_PER_BLOCK);
     const int64_t grid = p->n_units + zero_blocks;
     AGCN_REQUIRE(grid < (int64_t)INT32_MAX, "agcn_spmm_run: grid too large");
     const bool small_launch = p->n_units <= (int64_t)SPMM_SMALL_MIN_BLOCKS * p->sm_count;
+
     // Column panels.  The gather re-reads a row of X once per nonzero of that column, so it runs
     // at L2 speed only while the X columns of a pass stay L2-resident.  When dim > 64 and the
     // operand is somewhat larger than what L2 keeps, two 64-column passes (each re-streaming the
@@ -164,45 +206,64 @@ static int spmm_run(agcn_spmm_plan *p, const int *d_indices, const float *d_vals
     // When X is many times larger than L2 neither pass fits and one pass is as fast or faster
     // (6.3 against 6.5 ms at N = 5 000 000), so the split is limited to operands up to 4x L2.
     // Passes stay multiples of 32 columns so that every row segment is whole 128-byte lines.
-    // AGCN_SPMM_PANEL (read when the plan is created) overrides the choice.
+    // AGCN_SPMM_PANEL (read when the plan is created) overrides the choice.  (A product whose A is
+    // column-tiled -- agcn_spmm_tiled_* -- keeps its X slab in L2 by construction and never splits.)
     int panel = SPMM_PANEL;
-    if (dim > 64 && dim % 32 == 0 && ldx % 32 == 0) {
+    if (dim > 64 && dim % 32 == 0 && ldx_use % 32 == 0 && !accumulate && !p->never_split) {
         const int full = dim < SPMM_PANEL ? dim : SPMM_PANEL;
         const double x_bytes = (double)p->n_cols * full * 4.0;
         if (x_bytes > 0.75 * (double)p->l2_bytes && x_bytes <= 4.0 * (double)p->l2_bytes) panel = 64;
     }
     if (p->panel_override > 0) panel = p->panel_override;
     AGCN_REQUIRE(panel >= 1 && panel <= SPMM_PANEL, "agcn_spmm_run: AGCN_SPMM_PANEL must be 1..%d", SPMM_PANEL);
+    if (x_vec && panel % 4 != 0) panel = (panel + 3) & ~3;         // keep every panel's first column 16-byte aligned
+    if (panel > SPMM_PANEL) panel = SPMM_PANEL;
     for (int col0 = 0; col0 < dim; col0 += panel) {
         const int width = dim - col0 < panel ? dim - col0 : panel;
         SpmmParams prm;
         prm.block4 = p->block4; prm.n_blocks = p->n_blocks; prm.n_units = p->n_units;
         prm.idx = d_indices; prm.val = d_vals;
-        prm.x = d_x + col0; prm.ldx = ldx;
+        prm.x = x_use + col0; prm.ldx = ldx_use;
         prm.y = d_y + col0; prm.ldy = ldy;
-        prm.dim = width;
         prm.unit_carry = p->unit_carry; prm.carry = p->carry;
         prm.zero_rows = p->zero_rows; prm.n_zero_rows = p->n_zero;
         prm.relu = activation;
-        const bool vec = width % 4 == 0 && ldx % 4 == 0 && ldy % 4 == 0 && aligned16(prm.x) && aligned16(prm.y);
+        prm.accumulate = accumulate;
+        const bool vec = x_vec && aligned16(prm.x);
+        const bool y_vec = width % 4 == 0 && ldy % 4 == 0 && aligned16(prm.y);
+        prm.y_vec = y_vec ? 1 : 0;
+        prm.dim_store = width;
+        prm.dim = vec ? (width + 3) & ~3 : width;       // columns gathered (the padded copy holds zeros past dim)
+        const bool plain = !accumulate && (vec ? y_vec : true);
         if (grid > 0) {
-            if (!vec) launch_units<0>(prm, (unsigned)grid, small_launch, s);
-            else if (width <= 16) launch_units<4>(prm, (unsigned)grid, small_launch, s);
-            else if (width <= 32) launch_units<8>(prm, (unsigned)grid, small_launch, s);
-            else if (width <= 64) launch_units<16>(prm, (unsigned)grid, small_launch, s);
-            else launch_units<32>(prm, (unsigned)grid, small_launch, s);
+            launch_units_for_width(prm.dim, vec, prm, (unsigned)grid, small_launch, plain, s);
             AGCN_LAUNCH_CHECK("spmm_units_kernel");
             p->launches_last_run++;
         }
         if (p->n_carry > 0) {
             const unsigned cgrid = (unsigned)ceil_div(p->n_carry, SPMM_WARPS);
             auto k = vec ? spmm_carry_kernel<true> : spmm_carry_kernel<false>;
-            AGCN_KERNEL(k, cgrid, SPMM_THREADS, s, (const float *)p->carry, (const int *)p->carry_row, p->n_carry, prm.y, ldy, width, activation);
+            AGCN_KERNEL(k, cgrid, SPMM_THREADS, s, (const float *)p->carry, (const int *)p->carry_row, p->n_carry, prm.y, ldy,
+                        prm.dim, activation, accumulate, prm.y_vec, prm.dim_store);
             AGCN_LAUNCH_CHECK("spmm_carry_kernel");
             p->launches_last_run++;
         }
     }
     return AGCN_OK;
+}
+
+int spmm_run(agcn_spmm_plan *p, const int *d_indices, const float *d_vals, const float *d_x, int64_t ldx,
+             float *d_y, int64_t ldy, int dim, cudaStream_t s, int activation, int accumulate)
+{
+    int rc = spmm_check_run_args(p, d_indices, d_vals, d_x, ldx, d_y, ldy, dim, activation);
+    if (rc != AGCN_OK) return rc;
+    p->launches_last_run = 0;
+    const float *x_use = nullptr;
+    int64_t ldx_use = 0;
+    bool x_vec = false;
+    rc = spmm_prepare_x(p, d_x, ldx, dim, s, &x_use, &ldx_use, &x_vec);
+    if (rc != AGCN_OK) return rc;
+    return spmm_run_prepared(p, d_indices, d_vals, x_use, ldx_use, x_vec, d_y, ldy, dim, s, activation, accumulate);
 }
 
 }  // namespace agcn

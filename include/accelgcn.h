@@ -77,8 +77,11 @@ int agcn_partition_host(const int32_t *h_indptr, int64_t n_rows,
  * every GPU that loads the library until the process exits) and the call makes
  * no cudaMalloc / cudaFree or other allocating call.
  *  - n_rows above AGCN_PARTITION_NOALLOC_MAX_ROWS is AGCN_ERR_INVALID.
- *  - The first call on each device looks up the array's device address; make
- *    that first call before any stream capture begins.
+ *  - The first call on each device looks up the array's device address and, if
+ *    it is the library's first launch there, makes the CUDA runtime load the
+ *    kernels -- which may itself take device memory.  Make that first call at
+ *    start-up, before the host's allocator claims the GPU and before any stream
+ *    capture begins; calls after it leave the free-memory figure unchanged.
  *  - All calls on a GPU share the array: calls that overlap on the same GPU
  *    (other streams or threads) race and must be serialised by the caller. */
 #define AGCN_PARTITION_NOALLOC_MAX_ROWS 16777216   /* 2^24 */

@@ -30,9 +30,19 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB = None
 
-# Where the reference source tree is looked for when it is needed (building oracle/_ref,
-# regenerating fixtures, the live-script tests); absent on a GPU box, and nothing there needs it.
-REFERENCE_DIR = os.environ.get("ACCELGCN_REFERENCE", os.path.join(os.sep, "root", "reference"))
+# Where the reference source tree (an ICCAD-Accel-GCN checkout) lies, when it is needed: building
+# oracle/_ref, regenerating fixtures, the live-script tests.  Set ACCELGCN_REFERENCE to name it; when
+# the variable is unset a checkout placed beside this repository (../reference) is used if it exists.
+# Nothing that runs on a GPU box needs it, and everything that does skips cleanly when it is None.
+def _find_reference():
+    named = os.environ.get("ACCELGCN_REFERENCE")
+    if named:
+        return named if os.path.isfile(os.path.join(named, "block_level_partition.py")) else None
+    beside = os.path.normpath(os.path.join(_HERE, os.pardir, os.pardir, "reference"))
+    return beside if os.path.isfile(os.path.join(beside, "block_level_partition.py")) else None
+
+
+REFERENCE_DIR = _find_reference()
 
 DEG_BOUND = 12 * 32   # block_level_partition.py:7
 NUM_WARPS = 12        # block_level_partition.py:8

@@ -30,6 +30,9 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
 from oracle.oracle import REFERENCE_DIR as REF  # noqa: E402
 
+if REF is None:
+    sys.exit("make_golden.py needs the reference checkout: set ACCELGCN_REFERENCE=/path/to/ICCAD-Accel-GCN")
+
 
 def invert_block4(b):
     """.block4 tuples -> (leading zero rows, degrees[], counts[]) of the sorted degree sequence."""

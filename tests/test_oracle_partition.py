@@ -8,7 +8,7 @@ import pytest
 from conftest import kat_indptr, sha256_block4
 from oracle import oracle
 
-REFERENCE = oracle.REFERENCE_DIR
+REFERENCE = oracle.REFERENCE_DIR or ""        # "" when no reference checkout is around: the live tests skip
 
 
 def test_pattern_tables_closed_form():
@@ -42,7 +42,7 @@ def test_oracle_matches_reference_script_edge_cases(edge_cases):
         assert np.array_equal(oracle.partition_py(indptr), want), name
 
 
-@pytest.mark.skipif(not os.path.isdir(os.path.join(REFERENCE, "block_level_meta")), reason="reference tree not present")
+@pytest.mark.skipif(not (REFERENCE and os.path.isdir(os.path.join(REFERENCE, "block_level_meta"))), reason="reference tree not present")
 def test_kat_fixture_is_the_reference_files(kat):
     # the committed fixture really is the reference's goldens, byte for byte
     files = sorted(glob.glob(os.path.join(REFERENCE, "block_level_meta", "*.block4")))
@@ -80,7 +80,7 @@ def test_degree_sort_oracle_properties():
         assert np.array_equal(nval[nip[r]:nip[r + 1]], val[indptr[o]:indptr[o + 1]])
 
 
-@pytest.mark.skipif(not os.path.isfile(os.path.join(REFERENCE, "block_level_partition.py")), reason="reference tree not present")
+@pytest.mark.skipif(not (REFERENCE and os.path.isfile(os.path.join(REFERENCE, "block_level_partition.py"))), reason="reference tree not present")
 @pytest.mark.parametrize("seed", [0, 1, 2])
 def test_oracle_against_the_unmodified_script_run_live(seed, tmp_path):
     # fresh random degree sequences through the reference script itself (subprocess, scratch directory

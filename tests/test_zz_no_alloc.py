@@ -86,3 +86,27 @@ def test_noalloc_partition_errors_then_recovers():
     small = torch.zeros((1, 4), dtype=torch.int32, device=dev)
     rc = lib.agcn_partition_device_noalloc(good.data_ptr(), 4, small.data_ptr(), 1, ctypes.byref(n_blocks), None)
     assert rc == _lib.ERR_CAPACITY and n_blocks.value == 3
+
+
+def test_noalloc_partition_leaves_free_device_memory_unchanged():
+    # the property the entry point exists for: after one warm-up call (which may load the kernels),
+    # further calls take no device memory -- cudaMemGetInfo reads the same before and after
+    import torch
+    from accelgcn import _lib
+    dev = require_cuda()
+    lib = _lib.load()
+    rng = np.random.default_rng(7)
+    d_ip = torch.from_numpy(_indptr(rng, 300_000, [0, 1, 2, 5, 40, 200, 385, 3000])).to(dev)
+    n_blocks = ctypes.c_int64(0)
+    _lib.check(lib.agcn_partition_device_noalloc(d_ip.data_ptr(), 300_000, None, 0, ctypes.byref(n_blocks), None))
+    out = torch.empty((n_blocks.value, 4), dtype=torch.int32, device=dev)
+    _lib.check(lib.agcn_partition_device_noalloc(d_ip.data_ptr(), 300_000, out.data_ptr(), n_blocks.value,
+                                                 ctypes.byref(n_blocks), None))          # warm-up, full path
+    torch.cuda.synchronize()
+    free_before, _total = torch.cuda.mem_get_info(dev)
+    for _ in range(3):
+        _lib.check(lib.agcn_partition_device_noalloc(d_ip.data_ptr(), 300_000, out.data_ptr(), n_blocks.value,
+                                                     ctypes.byref(n_blocks), None))
+        assert torch.cuda.mem_get_info(dev)[0] == free_before
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info(dev)[0] == free_before
