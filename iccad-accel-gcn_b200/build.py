@@ -9,7 +9,7 @@ import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-SOURCES = ["common.cu", "partition.cu", "degree_sort.cu", "spmm.cu", "spmm_tiled.cu", "gemm.cu"]
+SOURCES = ["common.cu", "partition.cu", "degree_sort.cu", "spmm.cu", "spmm_tiled.cu", "host_spmm.cu", "gemm.cu", "layout.cu", "dist.cu", "probe.cu"]
 LIB = os.path.join(HERE, "lib", "libaccelgcn.so")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-shared"]
@@ -45,7 +45,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         return LIB
     os.makedirs(os.path.dirname(LIB), exist_ok=True)
     cmd = ["nvcc", *NVCC_FLAGS, *(["-Xptxas", "-v"] if verbose else []), "-o", LIB,
-           *[os.path.join(HERE, "csrc", s) for s in SOURCES]]
+           *[os.path.join(HERE, "csrc", s) for s in SOURCES], "-ldl"]
     subprocess.check_call(cmd)
     return LIB
 

@@ -2,9 +2,11 @@
 // The reference has no dense transform (it benchmarks the SpMM alone); this is the X*W step of a
 // GCN layer around that SpMM.
 #include "host_common.h"
+#include "internal.h"
 #include "kernels/gemm_tf32_kernels.cuh"
 
 #include <cudaTypedefs.h>
+#include <mutex>
 
 namespace agcn {
 
@@ -29,16 +31,25 @@ static int get_encode_fn(EncodeTiledFn *out)
     return AGCN_OK;
 }
 
-static int gemm_tf32(const float *d_h, int64_t ldh, const float *d_w, float *d_z, int64_t ldz, int64_t m_rows,
-                     int k_dim, int n_dim, cudaStream_t s)
+static const char *gemm_status_text(int status)
 {
-    AGCN_REQUIRE(d_h != nullptr && d_w != nullptr && d_z != nullptr, "agcn_gemm_tf32: null pointer");
+    return status == GEMM_ERR_TIMEOUT_PRODUCER ? "TMA producer" : status == GEMM_ERR_TIMEOUT_MMA ? "MMA issuer" : "epilogue";
+}
+
+// Checks the arguments, encodes the tensor map of H and launches.  Nothing is allocated and the
+// stream is not synchronised; *d_status (device, zeroed here on the stream) receives a GEMM_ERR_*
+// code if a pipeline wait runs out.
+static int gemm_tf32_launch(const float *d_h, int64_t ldh, const float *d_w, float *d_z, int64_t ldz, int64_t m_rows,
+                            int k_dim, int n_dim, int *d_status, cudaStream_t s, uint32_t spin_limit, int skip_first_load)
+{
+    AGCN_REQUIRE(d_h != nullptr && d_w != nullptr && d_z != nullptr && d_status != nullptr, "agcn_gemm_tf32: null pointer");
     AGCN_REQUIRE(k_dim == GEMM_DIM && n_dim == GEMM_DIM,
                  "agcn_gemm_tf32: only K = N = %d is built (got K = %d, N = %d)", GEMM_DIM, k_dim, n_dim);
     AGCN_REQUIRE(m_rows >= 0 && m_rows < ((int64_t)1 << 31) * GEMM_TILE_M / 2, "agcn_gemm_tf32: row count out of range");
     AGCN_REQUIRE(ldh >= GEMM_DIM && ldz >= GEMM_DIM && ldh % 4 == 0 && ldz % 4 == 0,
                  "agcn_gemm_tf32: row strides must be >= 128 and multiples of 4 floats");
     AGCN_REQUIRE(aligned16(d_h) && aligned16(d_z), "agcn_gemm_tf32: H and Z must be 16-byte aligned");
+    AGCN_CUDA(cudaMemsetAsync(d_status, 0, sizeof(int), s));
     if (m_rows == 0) return AGCN_OK;
 
     EncodeTiledFn encode = nullptr;
@@ -57,26 +68,61 @@ static int gemm_tf32(const float *d_h, int64_t ldh, const float *d_w, float *d_z
         return AGCN_ERR_CUDA;
     }
 
-    int dev = 0, sm_count = 0;
+    // per-device facts, looked up once
+    static int sm_count_of[64] = {};
+    int dev = 0;
     AGCN_CUDA(cudaGetDevice(&dev));
-    AGCN_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
-    AGCN_CUDA(cudaFuncSetAttribute(gemm_tf32_128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES));
-    DeviceScratch scratch;
-    AGCN_ALLOC(d_err, scratch, int, 1);
-    AGCN_CUDA(cudaMemsetAsync(d_err, 0, sizeof(int), s));
+    AGCN_REQUIRE(dev >= 0 && dev < 64, "agcn_gemm_tf32: device ordinal %d not supported", dev);
+    if (sm_count_of[dev] == 0) {
+        int sm_count = 0;
+        AGCN_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
+        AGCN_CUDA(cudaFuncSetAttribute(gemm_tf32_128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES));
+        sm_count_of[dev] = sm_count;
+    }
     const int n_tiles = (int)ceil_div(m_rows, GEMM_TILE_M);
-    const int grid = n_tiles < sm_count ? n_tiles : sm_count;
-    gemm_tf32_128_kernel<<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, s>>>(map, d_w, d_z, ldz, m_rows, n_tiles, d_err);
+    const int grid = n_tiles < sm_count_of[dev] ? n_tiles : sm_count_of[dev];
+    gemm_tf32_128_kernel<<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, s>>>(map, d_w, d_z, ldz, m_rows, n_tiles, d_status, spin_limit,
+                                                                      skip_first_load);
     AGCN_LAUNCH_CHECK("gemm_tf32_128_kernel");
-    int err = 0;
-    AGCN_CUDA(cudaMemcpyAsync(&err, d_err, sizeof(int), cudaMemcpyDeviceToHost, s));
+    return AGCN_OK;
+}
+
+// status word of the synchronous entry points: one per device, allocated on first use and kept
+static int gemm_status_word(int **out)
+{
+    static std::mutex mutex;
+    static int *word_of[64] = {};
+    int dev = 0;
+    AGCN_CUDA(cudaGetDevice(&dev));
+    AGCN_REQUIRE(dev >= 0 && dev < 64, "agcn_gemm_tf32: device ordinal %d not supported", dev);
+    std::lock_guard<std::mutex> lock(mutex);
+    if (word_of[dev] == nullptr) AGCN_CUDA(cudaMalloc(&word_of[dev], sizeof(int)));
+    *out = word_of[dev];
+    return AGCN_OK;
+}
+
+static int gemm_tf32_sync(const float *d_h, int64_t ldh, const float *d_w, float *d_z, int64_t ldz, int64_t m_rows,
+                          int k_dim, int n_dim, cudaStream_t s, uint32_t spin_limit, int skip_first_load)
+{
+    int *d_status = nullptr;
+    int rc = gemm_status_word(&d_status);
+    if (rc != AGCN_OK) return rc;
+    rc = gemm_tf32_launch(d_h, ldh, d_w, d_z, ldz, m_rows, k_dim, n_dim, d_status, s, spin_limit, skip_first_load);
+    if (rc != AGCN_OK) return rc;
+    int status = 0;
+    AGCN_CUDA(cudaMemcpyAsync(&status, d_status, sizeof(int), cudaMemcpyDeviceToHost, s));
     AGCN_CUDA(cudaStreamSynchronize(s));
-    if (err != 0) {
-        set_error("agcn_gemm_tf32: a pipeline wait ran out (%s); the output is incomplete",
-                  err == GEMM_ERR_TIMEOUT_PRODUCER ? "TMA producer" : err == GEMM_ERR_TIMEOUT_MMA ? "MMA issuer" : "epilogue");
+    if (status != 0) {
+        set_error("agcn_gemm_tf32: a pipeline wait ran out (%s); the output is incomplete", gemm_status_text(status));
         return AGCN_ERR_CUDA;
     }
     return AGCN_OK;
+}
+
+int gemm_tf32_async(const float *d_h, int64_t ldh, const float *d_w, float *d_z, int64_t ldz, int64_t m_rows,
+                    int *d_status, cudaStream_t s)
+{
+    return gemm_tf32_launch(d_h, ldh, d_w, d_z, ldz, m_rows, GEMM_DIM, GEMM_DIM, d_status, s, GEMM_SPIN_LIMIT, 0);
 }
 
 }  // namespace agcn
@@ -85,5 +131,23 @@ extern "C" int agcn_gemm_tf32(const float *d_h, int64_t ldh, const float *d_w, f
                               int64_t m_rows, int k_dim, int n_dim, void *stream)
 {
     agcn::clear_error();
-    return agcn::gemm_tf32(d_h, ldh, d_w, d_z, ldz, m_rows, k_dim, n_dim, static_cast<cudaStream_t>(stream));
+    return agcn::gemm_tf32_sync(d_h, ldh, d_w, d_z, ldz, m_rows, k_dim, n_dim, static_cast<cudaStream_t>(stream),
+                                agcn::GEMM_SPIN_LIMIT, 0);
+}
+
+extern "C" int agcn_gemm_tf32_async(const float *d_h, int64_t ldh, const float *d_w, float *d_z, int64_t ldz,
+                                    int64_t m_rows, int k_dim, int n_dim, int32_t *d_status, void *stream)
+{
+    agcn::clear_error();
+    return agcn::gemm_tf32_launch(d_h, ldh, d_w, d_z, ldz, m_rows, k_dim, n_dim, d_status, static_cast<cudaStream_t>(stream),
+                                  agcn::GEMM_SPIN_LIMIT, 0);
+}
+
+extern "C" int agcn_gemm_tf32_selftest_timeout(const float *d_h, int64_t ldh, const float *d_w, float *d_z, int64_t ldz,
+                                               int64_t m_rows, void *stream)
+{
+    agcn::clear_error();
+    // 4096 polls of about 100 ns: the starved wait gives up after well under a millisecond
+    return agcn::gemm_tf32_sync(d_h, ldh, d_w, d_z, ldz, m_rows, agcn::GEMM_DIM, agcn::GEMM_DIM,
+                                static_cast<cudaStream_t>(stream), 4096u, 1);
 }

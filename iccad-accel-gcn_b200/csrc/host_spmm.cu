@@ -1,0 +1,422 @@
+// Host-buffer SpMM: the plug-in for a harness whose arrays live in host memory (the split
+// follows SPMM_BASE: constructor = graph, run(dim) = one product; spmm_base.h:9-20,
+// spmm_accel.cu:104-139), pipelined over three streams.
+//
+// What crosses PCIe is fixed by the call (the graph, X per product up; Y per product down), so
+// the work is to keep both copy engines and the SMs busy at once:
+//  - uploads, kernels and downloads run on three streams chained by events;
+//  - a product is launched as several unit ranges (a unit = 8 consecutive tuples), and the rows a
+//    range completes are downloaded while the next range computes; rows that the carry kernel
+//    finishes (heavy rows crossing unit boundaries) come down after it;
+//  - when the graph itself is part of the call (agcn_spmm_host_batch), column ids and values are
+//    uploaded in the same ranges and every range is multiplied -- for all products -- as soon as
+//    it has arrived, so the kernels and the downloads hide under the upload of A.
+// One cudaMemcpyAsync per copy; pinned host memory gives full overlap (pageable memory works,
+// staged by the driver).
+#include "host_common.h"
+#include "internal.h"
+
+#include <algorithm>
+#include <new>
+#include <vector>
+
+namespace agcn {
+constexpr int HOST_SPMM_WARPS = 8;                    // tuples per unit (SPMM_WARPS of the kernels)
+constexpr int HOST_SPMM_PANEL = 128;                  // widest product that can be issued in unit ranges
+}
+
+struct agcn_host_ctx {
+    cudaStream_t s_up = nullptr, s_run = nullptr, s_down = nullptr;
+    void *graph[3] = {nullptr, nullptr, nullptr};     // block4, idx, val
+    size_t graph_cap[3] = {0, 0, 0};
+    std::vector<void *> xbuf, ybuf, cbuf;             // per product of a batch: X, Y, carry scratch
+    std::vector<size_t> xcap, ycap, ccap;
+    agcn_spmm_plan *plan = nullptr;                   // of the graph set last
+    int64_t n_rows = 0, n_cols = 0, nnz = 0, n_blocks = 0;
+    // unit ranges a product is issued in, with the first row / first nonzero of each boundary
+    std::vector<int64_t> part_unit, part_row, part_loc;
+    int64_t first_deferred_row = 0;                   // rows from here on are complete only after the carry kernel
+    int *d_abort = nullptr;                           // device word: set when a column id is out of range
+    std::vector<cudaEvent_t> events;
+    size_t events_used = 0;
+};
+
+namespace agcn {
+
+static int ctx_event(agcn_host_ctx *c, cudaEvent_t *out)
+{
+    if (c->events_used == c->events.size()) {
+        cudaEvent_t e = nullptr;
+        AGCN_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+        c->events.push_back(e);
+    }
+    *out = c->events[c->events_used++];
+    return AGCN_OK;
+}
+
+// `from` -> event -> `to`: everything enqueued on `to` afterwards runs after what `from` holds now
+static int ctx_chain(agcn_host_ctx *c, cudaStream_t from, cudaStream_t to)
+{
+    cudaEvent_t e = nullptr;
+    int rc = ctx_event(c, &e);
+    if (rc != AGCN_OK) return rc;
+    AGCN_CUDA(cudaEventRecord(e, from));
+    AGCN_CUDA(cudaStreamWaitEvent(to, e, 0));
+    return AGCN_OK;
+}
+
+static int reserve(void **buf, size_t *cap, size_t bytes)
+{
+    if (bytes <= *cap) return AGCN_OK;
+    if (*buf != nullptr) AGCN_CUDA(cudaFree(*buf));
+    *buf = nullptr; *cap = 0;
+    AGCN_CUDA(cudaMalloc(buf, bytes));
+    *cap = bytes;
+    return AGCN_OK;
+}
+
+static int ctx_sync(agcn_host_ctx *c)
+{
+    cudaError_t e1 = cudaStreamSynchronize(c->s_up), e2 = cudaStreamSynchronize(c->s_run), e3 = cudaStreamSynchronize(c->s_down);
+    c->events_used = 0;
+    const cudaError_t e = e1 != cudaSuccess ? e1 : e2 != cudaSuccess ? e2 : e3;
+    if (e != cudaSuccess) {
+        set_error("agcn_host_spmm: %s", cudaGetErrorString(e));
+        return AGCN_ERR_CUDA;
+    }
+    return AGCN_OK;
+}
+
+// Cuts the tuple list into about `want_parts` unit ranges of equal nonzero count, reading the
+// caller's host copy of .block4 (tuples tile [0, nnz) in order, so loc_begin is monotone).
+static void plan_parts(agcn_host_ctx *c, const int *h_block4, int want_parts)
+{
+    const int64_t n_units = ceil_div(c->n_blocks, HOST_SPMM_WARPS);
+    c->part_unit.assign(1, 0);
+    c->part_row.assign(1, 0);
+    c->part_loc.assign(1, 0);
+    if (want_parts < 1) want_parts = 1;
+    for (int k = 1; k < want_parts && n_units > 0; k++) {
+        const int64_t target = c->nnz * k / want_parts;
+        // first unit whose first tuple starts at or after `target`
+        int64_t lo = c->part_unit.back(), hi = n_units;
+        while (lo < hi) {
+            const int64_t mid = lo + (hi - lo) / 2;
+            if ((int64_t)h_block4[4 * mid * HOST_SPMM_WARPS + 2] < target) lo = mid + 1; else hi = mid;
+        }
+        if (lo <= c->part_unit.back() || lo >= n_units) continue;
+        c->part_unit.push_back(lo);
+        c->part_row.push_back(h_block4[4 * lo * HOST_SPMM_WARPS + 1]);
+        c->part_loc.push_back(h_block4[4 * lo * HOST_SPMM_WARPS + 2]);
+    }
+    c->part_unit.push_back(n_units);
+    c->part_row.push_back(c->n_rows);
+    c->part_loc.push_back(c->nnz);
+}
+
+static int check_graph_args(agcn_host_ctx *ctx, const int *h_block4, int64_t n_blocks, const int *h_indices,
+                            const float *h_vals, int64_t n_rows, int64_t n_cols, int64_t nnz)
+{
+    AGCN_REQUIRE(ctx != nullptr, "agcn_host_set_graph: null context");
+    AGCN_REQUIRE(n_blocks >= 0 && (n_blocks == 0 || h_block4 != nullptr), "agcn_host_set_graph: null block4");
+    AGCN_REQUIRE(nnz >= 0 && nnz <= (int64_t)INT32_MAX && (nnz == 0 || (h_indices != nullptr && h_vals != nullptr)),
+                 "agcn_host_set_graph: null indices or values, or nnz out of range");
+    AGCN_REQUIRE(n_rows > 0 && n_cols > 0, "agcn_host_set_graph: bad sizes");
+    return AGCN_OK;
+}
+
+// Uploads .block4 and builds the plan.  Column ids are validated by the caller of this function
+// (whole array, or range by range as they arrive).
+static int upload_block4_and_plan(agcn_host_ctx *c, const int *h_block4, int64_t n_blocks, int64_t n_rows, int64_t n_cols,
+                                  int64_t nnz)
+{
+    plan_free(c->plan);
+    c->plan = nullptr;
+    c->n_rows = n_rows; c->n_cols = n_cols; c->nnz = nnz; c->n_blocks = n_blocks;
+    const size_t bytes[3] = {(size_t)n_blocks * 16, (size_t)nnz * 4, (size_t)nnz * 4};
+    for (int i = 0; i < 3; i++) {
+        int rc = reserve(&c->graph[i], &c->graph_cap[i], bytes[i] > 0 ? bytes[i] : 16);
+        if (rc != AGCN_OK) return rc;
+    }
+    if (c->d_abort == nullptr) AGCN_CUDA(cudaMalloc(&c->d_abort, sizeof(int)));
+    AGCN_CUDA(cudaMemsetAsync(c->d_abort, 0, sizeof(int), c->s_run));
+    if (n_blocks > 0) AGCN_CUDA(cudaMemcpyAsync(c->graph[0], h_block4, bytes[0], cudaMemcpyHostToDevice, c->s_up));
+    int rc = ctx_chain(c, c->s_up, c->s_run);
+    if (rc != AGCN_OK) return rc;
+    // tuple validation, carry slots, uncovered rows (synchronises s_run)
+    rc = spmm_create(&c->plan, static_cast<const int *>(c->graph[0]), n_blocks, nullptr, n_rows, n_cols, nnz, c->s_run);
+    if (rc != AGCN_OK) return rc;
+    c->first_deferred_row = n_rows;
+    if (c->plan->n_carry > 0) {
+        int first = 0;       // carry slots are assigned in unit order, so their rows ascend
+        AGCN_CUDA(cudaMemcpyAsync(&first, c->plan->carry_row, sizeof(int), cudaMemcpyDeviceToHost, c->s_run));
+        AGCN_CUDA(cudaStreamSynchronize(c->s_run));
+        c->first_deferred_row = first;
+    }
+    return AGCN_OK;
+}
+
+static int host_set_graph(agcn_host_ctx *c, const int *h_block4, int64_t n_blocks, const int *h_indices,
+                          const float *h_vals, int64_t n_rows, int64_t n_cols, int64_t nnz)
+{
+    int rc = check_graph_args(c, h_block4, n_blocks, h_indices, h_vals, n_rows, n_cols, nnz);
+    if (rc != AGCN_OK) return rc;
+    // the column ids and values go up behind .block4 while the plan is being built from it
+    rc = reserve(&c->graph[1], &c->graph_cap[1], nnz > 0 ? (size_t)nnz * 4 : 16);
+    if (rc == AGCN_OK) rc = reserve(&c->graph[2], &c->graph_cap[2], nnz > 0 ? (size_t)nnz * 4 : 16);
+    if (rc == AGCN_OK) rc = reserve(&c->graph[0], &c->graph_cap[0], n_blocks > 0 ? (size_t)n_blocks * 16 : 16);
+    if (rc != AGCN_OK) return rc;
+    rc = upload_block4_and_plan(c, h_block4, n_blocks, n_rows, n_cols, nnz);
+    if (rc != AGCN_OK) return rc;
+    if (nnz > 0) {
+        AGCN_CUDA(cudaMemcpyAsync(c->graph[1], h_indices, (size_t)nnz * 4, cudaMemcpyHostToDevice, c->s_up));
+        rc = ctx_chain(c, c->s_up, c->s_run);
+        if (rc != AGCN_OK) return rc;
+        rc = spmm_check_cols(static_cast<const int *>(c->graph[1]), nnz, n_cols, c->d_abort, c->s_run);   // under the upload of the values
+        if (rc != AGCN_OK) return rc;
+        AGCN_CUDA(cudaMemcpyAsync(c->graph[2], h_vals, (size_t)nnz * 4, cudaMemcpyHostToDevice, c->s_up));
+    }
+    int bad = 0;
+    AGCN_CUDA(cudaMemcpyAsync(&bad, c->d_abort, sizeof(int), cudaMemcpyDeviceToHost, c->s_run));
+    rc = ctx_sync(c);
+    if (rc != AGCN_OK) return rc;
+    if (bad != 0) {
+        plan_free(c->plan);
+        c->plan = nullptr;
+        set_error("agcn_host_set_graph: invalid input: column index outside [0, n_cols);");
+        return AGCN_ERR_RANGE;
+    }
+    plan_parts(c, h_block4, 4);
+    return AGCN_OK;
+}
+
+static int reserve_products(agcn_host_ctx *c, int n, const int *dims, bool per_product_carry)
+{
+    if ((int)c->xbuf.size() < n) {
+        c->xbuf.resize(n, nullptr); c->ybuf.resize(n, nullptr); c->cbuf.resize(n, nullptr);
+        c->xcap.resize(n, 0); c->ycap.resize(n, 0); c->ccap.resize(n, 0);
+    }
+    for (int i = 0; i < n; i++) {
+        int rc = reserve(&c->xbuf[i], &c->xcap[i], (size_t)c->n_cols * dims[i] * 4);
+        if (rc == AGCN_OK) rc = reserve(&c->ybuf[i], &c->ycap[i], (size_t)c->n_rows * dims[i] * 4);
+        // products whose unit ranges interleave each keep their own partial sums of the heavy rows
+        if (rc == AGCN_OK && per_product_carry && c->plan->n_carry > 0)
+            rc = reserve(&c->cbuf[i], &c->ccap[i], (size_t)c->plan->n_carry * HOST_SPMM_PANEL * 4);
+        if (rc != AGCN_OK) return rc;
+    }
+    return AGCN_OK;
+}
+
+// rows [lo, hi) of product i: device -> host, on the download stream, after what s_run holds now
+static int download_rows(agcn_host_ctx *c, int i, float *h_y, int dim, int64_t lo, int64_t hi)
+{
+    if (hi <= lo) return AGCN_OK;
+    AGCN_CUDA(cudaMemcpyAsync(h_y + lo * dim, static_cast<const float *>(c->ybuf[i]) + lo * dim, (size_t)(hi - lo) * dim * 4,
+                              cudaMemcpyDeviceToHost, c->s_down));
+    return AGCN_OK;
+}
+
+static bool can_issue_in_parts(int dim) { return dim <= HOST_SPMM_PANEL && dim % 4 == 0; }
+
+// Products on a graph that is already on the device: X_i up, product i in unit ranges, rows down as
+// they complete.
+static int host_products(agcn_host_ctx *c, int n, const float *const *h_x, float *const *h_y, const int *dims)
+{
+    AGCN_REQUIRE(c != nullptr && c->plan != nullptr, "agcn_host_spmm: no graph set (call agcn_host_set_graph first)");
+    AGCN_REQUIRE(n >= 0 && (n == 0 || (h_x != nullptr && h_y != nullptr && dims != nullptr)), "agcn_host_spmm: null argument");
+    for (int i = 0; i < n; i++)
+        AGCN_REQUIRE(h_x[i] != nullptr && h_y[i] != nullptr && dims[i] >= 1, "agcn_host_spmm: null X or Y, or dim < 1");
+    if (n == 0) return AGCN_OK;
+    int rc = reserve_products(c, n, dims, false);
+    if (rc != AGCN_OK) return rc;
+    const int *idx = static_cast<const int *>(c->graph[1]);
+    const float *val = static_cast<const float *>(c->graph[2]);
+    std::vector<cudaEvent_t> x_up(n);
+    for (int i = 0; i < n; i++) {
+        AGCN_CUDA(cudaMemcpyAsync(c->xbuf[i], h_x[i], (size_t)c->n_cols * dims[i] * 4, cudaMemcpyHostToDevice, c->s_up));
+        rc = ctx_event(c, &x_up[i]);
+        if (rc != AGCN_OK) return rc;
+        AGCN_CUDA(cudaEventRecord(x_up[i], c->s_up));
+    }
+    const int n_parts = (int)c->part_unit.size() - 1;
+    for (int i = 0; i < n; i++) {
+        const int dim = dims[i];
+        float *y = static_cast<float *>(c->ybuf[i]);
+        AGCN_CUDA(cudaStreamWaitEvent(c->s_run, x_up[i], 0));
+        if (!can_issue_in_parts(dim) || n_parts <= 1) {
+            rc = spmm_run(c->plan, idx, val, static_cast<const float *>(c->xbuf[i]), dim, y, dim, dim, c->s_run);
+            if (rc == AGCN_OK) rc = ctx_chain(c, c->s_run, c->s_down);
+            if (rc == AGCN_OK) rc = download_rows(c, i, h_y[i], dim, 0, c->n_rows);
+            if (rc != AGCN_OK) { ctx_sync(c); return rc; }
+            continue;
+        }
+        for (int k = 0; k < n_parts; k++) {
+            SpmmLaunchPart part;
+            part.unit0 = c->part_unit[k]; part.unit1 = c->part_unit[k + 1];
+            part.zero_fill = k == 0; part.carry = false;
+            rc = spmm_run_prepared(c->plan, idx, val, static_cast<const float *>(c->xbuf[i]), dim, true, y, dim, dim, c->s_run, 0, 0, part);
+            if (rc == AGCN_OK) rc = ctx_chain(c, c->s_run, c->s_down);
+            if (rc == AGCN_OK) rc = download_rows(c, i, h_y[i], dim, c->part_row[k], std::min(c->part_row[k + 1], c->first_deferred_row));
+            if (rc != AGCN_OK) { ctx_sync(c); return rc; }
+        }
+        SpmmLaunchPart tail;                  // no units: only the carry kernel
+        tail.unit0 = tail.unit1 = c->plan->n_units; tail.zero_fill = false; tail.carry = true;
+        rc = spmm_run_prepared(c->plan, idx, val, static_cast<const float *>(c->xbuf[i]), dim, true, y, dim, dim, c->s_run, 0, 0, tail);
+        if (rc == AGCN_OK) rc = ctx_chain(c, c->s_run, c->s_down);
+        if (rc == AGCN_OK) rc = download_rows(c, i, h_y[i], dim, c->first_deferred_row, c->n_rows);
+        if (rc != AGCN_OK) { ctx_sync(c); return rc; }
+    }
+    return ctx_sync(c);
+}
+
+// The graph and the products in one call: A is uploaded in unit ranges and every range is
+// multiplied for all products as soon as it is on the device.
+static int host_graph_and_products(agcn_host_ctx *c, const int *h_block4, int64_t n_blocks, const int *h_indices,
+                                   const float *h_vals, int64_t n_rows, int64_t n_cols, int64_t nnz, int n,
+                                   const float *const *h_x, float *const *h_y, const int *dims)
+{
+    int rc = check_graph_args(c, h_block4, n_blocks, h_indices, h_vals, n_rows, n_cols, nnz);
+    if (rc != AGCN_OK) return rc;
+    AGCN_REQUIRE(n >= 0 && (n == 0 || (h_x != nullptr && h_y != nullptr && dims != nullptr)), "agcn_spmm_host_batch: null argument");
+    bool stream_a = n > 0 && nnz > 0 && n_blocks > 0;
+    for (int i = 0; i < n; i++) {
+        AGCN_REQUIRE(h_x[i] != nullptr && h_y[i] != nullptr && dims[i] >= 1, "agcn_spmm_host_batch: null X or Y, or dim < 1");
+        stream_a = stream_a && can_issue_in_parts(dims[i]);
+    }
+    if (!stream_a) {         // widths the unit-range launch does not take: graph first, then the products
+        rc = host_set_graph(c, h_block4, n_blocks, h_indices, h_vals, n_rows, n_cols, nnz);
+        return rc != AGCN_OK ? rc : host_products(c, n, h_x, h_y, dims);
+    }
+    rc = upload_block4_and_plan(c, h_block4, n_blocks, n_rows, n_cols, nnz);
+    if (rc != AGCN_OK) return rc;
+    rc = reserve_products(c, n, dims, true);
+    if (rc != AGCN_OK) return rc;
+    // ranges of about 32 MB of (column id, value) pairs: long enough for full PCIe speed, short
+    // enough that the first product starts early and the last download is short
+    plan_parts(c, h_block4, (int)std::max<int64_t>(1, std::min<int64_t>(64, (nnz * 8) >> 25)));
+    const int n_parts = (int)c->part_unit.size() - 1;
+    int *idx = static_cast<int *>(c->graph[1]);
+    float *val = static_cast<float *>(c->graph[2]);
+    for (int i = 0; i < n; i++)
+        AGCN_CUDA(cudaMemcpyAsync(c->xbuf[i], h_x[i], (size_t)n_cols * dims[i] * 4, cudaMemcpyHostToDevice, c->s_up));
+    for (int k = 0; k < n_parts; k++) {
+        const int64_t p0 = c->part_loc[k], p1 = c->part_loc[k + 1];
+        AGCN_CUDA(cudaMemcpyAsync(idx + p0, h_indices + p0, (size_t)(p1 - p0) * 4, cudaMemcpyHostToDevice, c->s_up));
+        AGCN_CUDA(cudaMemcpyAsync(val + p0, h_vals + p0, (size_t)(p1 - p0) * 4, cudaMemcpyHostToDevice, c->s_up));
+        rc = ctx_chain(c, c->s_up, c->s_run);
+        // a column id outside [0, n_cols) sets the abort word, and every kernel behind it returns at once
+        if (rc == AGCN_OK) rc = spmm_check_cols(idx + p0, p1 - p0, n_cols, c->d_abort, c->s_run);
+        for (int i = 0; i < n && rc == AGCN_OK; i++) {
+            SpmmLaunchPart part;
+            part.unit0 = c->part_unit[k]; part.unit1 = c->part_unit[k + 1];
+            part.zero_fill = k == 0; part.carry = false; part.abort_flag = c->d_abort;
+            part.carry_buf = static_cast<float *>(c->cbuf[i]);
+            rc = spmm_run_prepared(c->plan, idx, val, static_cast<const float *>(c->xbuf[i]), dims[i], true,
+                                   static_cast<float *>(c->ybuf[i]), dims[i], dims[i], c->s_run, 0, 0, part);
+        }
+        if (rc == AGCN_OK) rc = ctx_chain(c, c->s_run, c->s_down);
+        for (int i = 0; i < n && rc == AGCN_OK; i++)
+            rc = download_rows(c, i, h_y[i], dims[i], c->part_row[k], std::min(c->part_row[k + 1], c->first_deferred_row));
+        if (rc != AGCN_OK) { ctx_sync(c); return rc; }
+    }
+    for (int i = 0; i < n; i++) {
+        SpmmLaunchPart tail;
+        tail.unit0 = tail.unit1 = c->plan->n_units; tail.zero_fill = false; tail.carry = true; tail.abort_flag = c->d_abort;
+        tail.carry_buf = static_cast<float *>(c->cbuf[i]);
+        rc = spmm_run_prepared(c->plan, idx, val, static_cast<const float *>(c->xbuf[i]), dims[i], true,
+                               static_cast<float *>(c->ybuf[i]), dims[i], dims[i], c->s_run, 0, 0, tail);
+        if (rc != AGCN_OK) { ctx_sync(c); return rc; }
+    }
+    rc = ctx_chain(c, c->s_run, c->s_down);
+    for (int i = 0; i < n && rc == AGCN_OK; i++) rc = download_rows(c, i, h_y[i], dims[i], c->first_deferred_row, n_rows);
+    int bad = 0;
+    if (rc == AGCN_OK && cudaMemcpyAsync(&bad, c->d_abort, sizeof(int), cudaMemcpyDeviceToHost, c->s_run) != cudaSuccess) rc = AGCN_ERR_CUDA;
+    const int rc_sync = ctx_sync(c);
+    if (rc != AGCN_OK || rc_sync != AGCN_OK) return rc != AGCN_OK ? rc : rc_sync;
+    if (bad != 0) {
+        plan_free(c->plan);
+        c->plan = nullptr;
+        set_error("agcn_spmm_host_batch: invalid input: column index outside [0, n_cols); the products were not computed");
+        return AGCN_ERR_RANGE;
+    }
+    plan_parts(c, h_block4, 4);         // later agcn_host_spmm calls on this graph use a few large ranges
+    return AGCN_OK;
+}
+
+}  // namespace agcn
+
+extern "C" int agcn_host_ctx_create(agcn_host_ctx **ctx)
+{
+    using namespace agcn;
+    clear_error();
+    AGCN_REQUIRE(ctx != nullptr, "agcn_host_ctx_create: null pointer");
+    *ctx = nullptr;
+    agcn_host_ctx *c = new (std::nothrow) agcn_host_ctx;
+    AGCN_REQUIRE(c != nullptr, "agcn_host_ctx_create: out of host memory");
+    cudaError_t e = cudaStreamCreateWithFlags(&c->s_up, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&c->s_run, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&c->s_down, cudaStreamNonBlocking);
+    if (e != cudaSuccess) {
+        agcn_host_ctx_destroy(c);
+        set_error("agcn_host_ctx_create: cudaStreamCreate: %s", cudaGetErrorString(e));
+        return AGCN_ERR_CUDA;
+    }
+    *ctx = c;
+    return AGCN_OK;
+}
+
+extern "C" int agcn_host_ctx_destroy(agcn_host_ctx *ctx)
+{
+    agcn::clear_error();
+    if (ctx == nullptr) return AGCN_OK;
+    agcn::plan_free(ctx->plan);
+    for (int i = 0; i < 3; i++) cudaFree(ctx->graph[i]);
+    for (void *p : ctx->xbuf) cudaFree(p);
+    for (void *p : ctx->ybuf) cudaFree(p);
+    for (void *p : ctx->cbuf) cudaFree(p);
+    cudaFree(ctx->d_abort);
+    for (cudaEvent_t e : ctx->events) cudaEventDestroy(e);
+    if (ctx->s_up) cudaStreamDestroy(ctx->s_up);
+    if (ctx->s_run) cudaStreamDestroy(ctx->s_run);
+    if (ctx->s_down) cudaStreamDestroy(ctx->s_down);
+    delete ctx;
+    return AGCN_OK;
+}
+
+extern "C" int agcn_host_set_graph(agcn_host_ctx *ctx, const int32_t *h_block4, int64_t n_blocks,
+                                   const int32_t *h_indices, const float *h_vals,
+                                   int64_t n_rows, int64_t n_cols, int64_t nnz)
+{
+    agcn::clear_error();
+    return agcn::host_set_graph(ctx, h_block4, n_blocks, h_indices, h_vals, n_rows, n_cols, nnz);
+}
+
+extern "C" int agcn_host_spmm(agcn_host_ctx *ctx, const float *h_x, float *h_y, int dim)
+{
+    agcn::clear_error();
+    return agcn::host_products(ctx, 1, &h_x, &h_y, &dim);
+}
+
+extern "C" int agcn_host_spmm_batch(agcn_host_ctx *ctx, int n_products, const float *const *h_x, float *const *h_y,
+                                    const int *dims)
+{
+    agcn::clear_error();
+    return agcn::host_products(ctx, n_products, h_x, h_y, dims);
+}
+
+extern "C" int agcn_spmm_host(agcn_host_ctx *ctx, const int32_t *h_block4, int64_t n_blocks,
+                              const int32_t *h_indices, const float *h_vals, const float *h_x, float *h_y,
+                              int64_t n_rows, int64_t n_cols, int64_t nnz, int dim)
+{
+    agcn::clear_error();
+    return agcn::host_graph_and_products(ctx, h_block4, n_blocks, h_indices, h_vals, n_rows, n_cols, nnz, 1, &h_x, &h_y, &dim);
+}
+
+extern "C" int agcn_spmm_host_batch(agcn_host_ctx *ctx, const int32_t *h_block4, int64_t n_blocks,
+                                    const int32_t *h_indices, const float *h_vals,
+                                    int64_t n_rows, int64_t n_cols, int64_t nnz,
+                                    int n_products, const float *const *h_x, float *const *h_y, const int *dims)
+{
+    agcn::clear_error();
+    return agcn::host_graph_and_products(ctx, h_block4, n_blocks, h_indices, h_vals, n_rows, n_cols, nnz, n_products, h_x, h_y, dims);
+}

@@ -35,8 +35,28 @@ int spmm_check_run_args(const agcn_spmm_plan *p, const int *d_indices, const flo
                         const float *d_y, int64_t ldy, int dim, int activation);
 int spmm_prepare_x(agcn_spmm_plan *p, const float *d_x, int64_t ldx, int dim, cudaStream_t s,
                    const float **x_use, int64_t *ldx_use, bool *x_vec);
+// Which part of a product one call of spmm_run_prepared launches.  A product may be issued as
+// several unit ranges (a unit = 8 consecutive tuples = one thread block): the zero-fill of
+// uncovered rows goes with one of them and the carry kernel, which finishes the heavy rows that
+// cross unit boundaries, after the last.
+struct SpmmLaunchPart {
+    int64_t unit0 = 0, unit1 = -1;      // units [unit0, unit1); -1 = to the end
+    bool zero_fill = true, carry = true;
+    const int *abort_flag = nullptr;    // optional device word: nonzero makes the kernels return at once
+    float *carry_buf = nullptr;         // optional carry scratch [n_carry][128] to use instead of the plan's (products in flight together)
+};
 int spmm_run_prepared(agcn_spmm_plan *p, const int *d_indices, const float *d_vals, const float *x_use, int64_t ldx_use,
-                      bool x_vec, float *d_y, int64_t ldy, int dim, cudaStream_t s, int activation, int accumulate);
+                      bool x_vec, float *d_y, int64_t ldy, int dim, cudaStream_t s, int activation, int accumulate,
+                      const SpmmLaunchPart &part);
+int spmm_check_cols(const int *d_idx, int64_t count, int64_t n_cols, int *d_flag, cudaStream_t s);
 void plan_free(agcn_spmm_plan *p);
+
+
+// gemm.cu: Z = H * W (128 x 128, TF32) enqueued on `s`; nothing allocated, nothing synchronised
+int gemm_tf32_async(const float *d_h, int64_t ldh, const float *d_w, float *d_z, int64_t ldz, int64_t m_rows,
+                    int *d_status, cudaStream_t s);
+
+// layout.cu
+int balanced_blocks(const int *h_indptr, int64_t n_rows, int world, int64_t *h_ranges, int64_t *rows_per_block);
 
 }  // namespace agcn

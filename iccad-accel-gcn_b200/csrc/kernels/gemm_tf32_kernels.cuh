@@ -67,9 +67,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
     return ok != 0;
 }
 // Bounded wait.  Returns false if the barrier did not complete or the CTA is aborting.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag)
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, uint32_t spin_limit)
 {
-    for (uint32_t spin = 0; spin < GEMM_SPIN_LIMIT; spin++) {
+    for (uint32_t spin = 0; spin < spin_limit; spin++) {
         if (mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
         if (spin > 64) __nanosleep(100);
@@ -148,8 +148,12 @@ constexpr uint32_t GEMM_IDESC = (1u << 4)                 /* D format: f32 */
 
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tf32_128_kernel(const __grid_constant__ CUtensorMap map_h, const float *__restrict__ w,
-                     float *__restrict__ z, int64_t ldz, int64_t m_rows, int n_tiles, int *__restrict__ err_flag)
+                     float *__restrict__ z, int64_t ldz, int64_t m_rows, int n_tiles, int *__restrict__ err_flag,
+                     uint32_t spin_limit, int skip_first_load)
 {
+    // spin_limit: polls a wait may take (GEMM_SPIN_LIMIT in normal use).  skip_first_load: self-test
+    // of the failure path only -- the producer leaves out the first load of the thread block, so the
+    // MMA issuer's wait for it runs out and the kernel must leave through the abort path.
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t *s_w = smem;                                           // 64 KiB, K-major, swizzled
@@ -199,10 +203,11 @@ gemm_tf32_128_kernel(const __grid_constant__ CUtensorMap map_h, const float *__r
                 const int tile = (int)blockIdx.x + it * (int)gridDim.x;
                 for (int kb = 0; kb < GEMM_KBLKS; kb++, g++) {
                     const uint32_t s = g % GEMM_STAGES, ph = (g / GEMM_STAGES) & 1;
-                    if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1, s_abort)) {
+                    if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1, s_abort, spin_limit)) {
                         if (!*s_abort) { atomicExch(err_flag, GEMM_ERR_TIMEOUT_PRODUCER); *s_abort = 1; }
                         break;
                     }
+                    if (skip_first_load && g == 0) continue;      // self-test: this stage never fills
                     mbar_arrive_expect_tx(smem_u32(&bar_full[s]), GEMM_STAGE_BYTES);
                     tma_load_2d(smem_u32(s_ring + s * GEMM_STAGE_BYTES), &map_h, kb * GEMM_KBLK, tile * GEMM_TILE_M,
                                 smem_u32(&bar_full[s]));
@@ -212,7 +217,7 @@ gemm_tf32_128_kernel(const __grid_constant__ CUtensorMap map_h, const float *__r
                 // copies already issued still land in shared memory: give each stage a bounded chance to finish
                 for (uint32_t back = 0; back < GEMM_STAGES && back < g; back++) {
                     const uint32_t gg = g - 1 - back;
-                    mbar_wait(smem_u32(&bar_full[gg % GEMM_STAGES]), (gg / GEMM_STAGES) & 1, s_never);
+                    mbar_wait(smem_u32(&bar_full[gg % GEMM_STAGES]), (gg / GEMM_STAGES) & 1, s_never, spin_limit);
                 }
             }
         }
@@ -222,7 +227,7 @@ gemm_tf32_128_kernel(const __grid_constant__ CUtensorMap map_h, const float *__r
             uint32_t g = 0;
             for (int it = 0; it < my_tiles && !*s_abort; it++) {
                 const uint32_t acc = it & 1, acc_ph = (it >> 1) & 1;
-                if (!mbar_wait(smem_u32(&bar_acc_empty[acc]), acc_ph ^ 1, s_abort)) {
+                if (!mbar_wait(smem_u32(&bar_acc_empty[acc]), acc_ph ^ 1, s_abort, spin_limit)) {
                     if (!*s_abort) { atomicExch(err_flag, GEMM_ERR_TIMEOUT_MMA); *s_abort = 1; }
                     break;
                 }
@@ -231,7 +236,7 @@ gemm_tf32_128_kernel(const __grid_constant__ CUtensorMap map_h, const float *__r
                 bool ok = true;
                 for (int kb = 0; kb < GEMM_KBLKS; kb++, g++) {
                     const uint32_t s = g % GEMM_STAGES, ph = (g / GEMM_STAGES) & 1;
-                    if (!mbar_wait(smem_u32(&bar_full[s]), ph, s_abort)) { ok = false; break; }
+                    if (!mbar_wait(smem_u32(&bar_full[s]), ph, s_abort, spin_limit)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t a_addr = smem_u32(s_ring + s * GEMM_STAGE_BYTES);
                     const uint32_t b_addr = smem_u32(s_w + kb * GEMM_STAGE_BYTES);
@@ -257,7 +262,7 @@ gemm_tf32_128_kernel(const __grid_constant__ CUtensorMap map_h, const float *__r
         for (int it = 0; it < my_tiles && !*s_abort; it++) {
             const int tile = (int)blockIdx.x + it * (int)gridDim.x;
             const uint32_t acc = it & 1, acc_ph = (it >> 1) & 1;
-            if (!mbar_wait(smem_u32(&bar_acc_full[acc]), acc_ph, s_abort)) {
+            if (!mbar_wait(smem_u32(&bar_acc_full[acc]), acc_ph, s_abort, spin_limit)) {
                 if (!*s_abort) { atomicExch(err_flag, GEMM_ERR_TIMEOUT_EPILOGUE); *s_abort = 1; }
                 break;
             }

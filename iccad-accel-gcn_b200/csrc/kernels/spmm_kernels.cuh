@@ -50,7 +50,9 @@ constexpr int SPMM_SMALL_MIN_BLOCKS = 16 / SPMM_WARPS;
 struct SpmmParams {
     const int4 *block4;
     int64_t n_blocks;
-    int64_t n_units;
+    int64_t n_units;          // units of this launch (thread blocks beyond them zero-fill uncovered rows)
+    int64_t unit_base;        // first unit of this launch: a product may be launched as several unit ranges
+    const int *abort_flag;    // optional: a nonzero word makes every thread block return at once
     const int *idx;
     const float *val;
     const float *x;     // first column of the panel
@@ -243,6 +245,7 @@ spmm_units_kernel(const SpmmParams p)
     const bool active = col < p.dim;
     const L2Policies pol = make_l2_policies();
 
+    if (p.abort_flag != nullptr && *p.abort_flag != 0) return;     // input rejected by a check earlier in the stream
     if ((int64_t)blockIdx.x >= p.n_units) {
         // zero-fill rows that no tuple covers
         // (when accumulating, these rows keep their value and only the activation is applied)
@@ -259,7 +262,8 @@ spmm_units_kernel(const SpmmParams p)
         return;
     }
 
-    const int64_t e = (int64_t)blockIdx.x * SPMM_WARPS + w;
+    const int64_t unit = p.unit_base + blockIdx.x;
+    const int64_t e = unit * SPMM_WARPS + w;
     const TupleView t = decode_tuple(p.block4, e, p.n_blocks);
     const int total = t.n_rows * t.row_nz;
 
@@ -323,9 +327,9 @@ spmm_units_kernel(const SpmmParams p)
     if (w > 0 && s_big[w - 1] && s_row[w - 1] == t.row0) return;   // not the first tuple of its row here
     int w_end = w + 1;
     while (w_end < SPMM_WARPS && s_big[w_end] && s_row[w_end] == t.row0) w_end++;
-    const int64_t left = p.n_blocks - (int64_t)blockIdx.x * SPMM_WARPS;
+    const int64_t left = p.n_blocks - unit * SPMM_WARPS;
     const int w_last = left < SPMM_WARPS ? (int)left - 1 : SPMM_WARPS - 1;
-    const int2 uc = __ldg(p.unit_carry + blockIdx.x);
+    const int2 uc = __ldg(p.unit_carry + unit);
     const bool enters = w == 0 && uc.x >= 0;            // the row began in an earlier unit
     const bool leaves = w_end - 1 == w_last && uc.y >= 0;   // the row goes on in the next unit
     const bool partial = enters || leaves;     // the row is finished by spmm_carry_kernel

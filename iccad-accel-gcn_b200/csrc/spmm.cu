@@ -53,9 +53,8 @@ int spmm_create(agcn_spmm_plan **out, const int *d_block4, int64_t n_blocks, con
     AGCN_KERNEL(plan_check_kernel, (unsigned)ceil_div(n_blocks + 1, 256), 256, s, block4, n_blocks, n_rows, nnz, gap, d_err);
     AGCN_LAUNCH_CHECK("plan_check_kernel");
     if (d_indices != nullptr && nnz > 0) {
-        const int64_t blocks = ceil_div(nnz, 256 * 16);
-        AGCN_KERNEL(plan_check_cols_kernel, (unsigned)(blocks < 65535 ? blocks : 65535), 256, s, d_indices, nnz, n_cols, d_err);
-        AGCN_LAUNCH_CHECK("plan_check_cols_kernel");
+        int rc_cols = spmm_check_cols(d_indices, nnz, n_cols, d_err, s);
+        if (rc_cols != AGCN_OK) return rc_cols;
     }
     int rc = exclusive_scan_i32_i64(gap, gap_offset, n_blocks + 1, tile_sums, d_res + 0, s);
     if (rc != AGCN_OK) return rc;
@@ -115,6 +114,16 @@ int spmm_create(agcn_spmm_plan **out, const int *d_block4, int64_t n_blocks, con
         p->pad_unaligned = env_int("AGCN_SPMM_PAD", 1);
     }
     *out = p;
+    return AGCN_OK;
+}
+
+// Column ids idx[0 .. count) against [0, n_cols): ORs SPMM_ERR_COL into *d_flag when one is outside.
+int spmm_check_cols(const int *d_idx, int64_t count, int64_t n_cols, int *d_flag, cudaStream_t s)
+{
+    if (count <= 0) return AGCN_OK;
+    const int64_t blocks = ceil_div(count, 256 * 16);
+    AGCN_KERNEL(plan_check_cols_kernel, (unsigned)(blocks < 65535 ? blocks : 65535), 256, s, d_idx, count, n_cols, d_flag);
+    AGCN_LAUNCH_CHECK("plan_check_cols_kernel");
     return AGCN_OK;
 }
 
@@ -190,11 +199,14 @@ int spmm_check_run_args(const agcn_spmm_plan *p, const int *d_indices, const flo
 // range of a column-tiled product; rows no tuple covers then keep their value, and only get the
 // activation).
 int spmm_run_prepared(agcn_spmm_plan *p, const int *d_indices, const float *d_vals, const float *x_use, int64_t ldx_use,
-                      bool x_vec, float *d_y, int64_t ldy, int dim, cudaStream_t s, int activation, int accumulate)
+                      bool x_vec, float *d_y, int64_t ldy, int dim, cudaStream_t s, int activation, int accumulate,
+                      const SpmmLaunchPart &part)
 {
+    const int64_t unit0 = part.unit0, unit1 = part.unit1 < 0 ? p->n_units : part.unit1;
+    AGCN_REQUIRE(unit0 >= 0 && unit0 <= unit1 && unit1 <= p->n_units, "agcn_spmm_run: unit range outside the plan");
     // rows no tuple covers: zero-filled -- or, when accumulating, left alone unless an activation is due
-    const int64_t zero_blocks = accumulate && !activation ? 0 : ceil_div(p->n_zero, SPMM_ZERO_ROWS_PER_BLOCK);
-    const int64_t grid = p->n_units + zero_blocks;
+    const int64_t zero_blocks = !part.zero_fill || (accumulate && !activation) ? 0 : ceil_div(p->n_zero, SPMM_ZERO_ROWS_PER_BLOCK);
+    const int64_t grid = (unit1 - unit0) + zero_blocks;
     AGCN_REQUIRE(grid < (int64_t)INT32_MAX, "agcn_spmm_run: grid too large");
     const bool small_launch = p->n_units <= (int64_t)SPMM_SMALL_MIN_BLOCKS * p->sm_count;
 
@@ -215,17 +227,25 @@ int spmm_run_prepared(agcn_spmm_plan *p, const int *d_indices, const float *d_va
         if (x_bytes > 0.75 * (double)p->l2_bytes && x_bytes <= 4.0 * (double)p->l2_bytes) panel = 64;
     }
     if (p->panel_override > 0) panel = p->panel_override;
+    const bool whole = unit0 == 0 && unit1 == p->n_units && part.carry;
+    if (!whole) {
+        // the carry scratch holds the partial sums of ONE column panel between the unit launches and
+        // the carry kernel: a product issued in parts therefore runs as a single panel
+        AGCN_REQUIRE(dim <= SPMM_PANEL, "agcn_spmm_run: a product issued in unit ranges is limited to %d columns", SPMM_PANEL);
+        panel = SPMM_PANEL;
+    }
     AGCN_REQUIRE(panel >= 1 && panel <= SPMM_PANEL, "agcn_spmm_run: AGCN_SPMM_PANEL must be 1..%d", SPMM_PANEL);
     if (x_vec && panel % 4 != 0) panel = (panel + 3) & ~3;         // keep every panel's first column 16-byte aligned
     if (panel > SPMM_PANEL) panel = SPMM_PANEL;
     for (int col0 = 0; col0 < dim; col0 += panel) {
         const int width = dim - col0 < panel ? dim - col0 : panel;
         SpmmParams prm;
-        prm.block4 = p->block4; prm.n_blocks = p->n_blocks; prm.n_units = p->n_units;
+        prm.block4 = p->block4; prm.n_blocks = p->n_blocks;
+        prm.n_units = unit1 - unit0; prm.unit_base = unit0; prm.abort_flag = part.abort_flag;
         prm.idx = d_indices; prm.val = d_vals;
         prm.x = x_use + col0; prm.ldx = ldx_use;
         prm.y = d_y + col0; prm.ldy = ldy;
-        prm.unit_carry = p->unit_carry; prm.carry = p->carry;
+        prm.unit_carry = p->unit_carry; prm.carry = part.carry_buf != nullptr ? part.carry_buf : p->carry;
         prm.zero_rows = p->zero_rows; prm.n_zero_rows = p->n_zero;
         prm.relu = activation;
         prm.accumulate = accumulate;
@@ -240,10 +260,10 @@ int spmm_run_prepared(agcn_spmm_plan *p, const int *d_indices, const float *d_va
             AGCN_LAUNCH_CHECK("spmm_units_kernel");
             p->launches_last_run++;
         }
-        if (p->n_carry > 0) {
+        if (p->n_carry > 0 && part.carry) {
             const unsigned cgrid = (unsigned)ceil_div(p->n_carry, SPMM_WARPS);
             auto k = vec ? spmm_carry_kernel<true> : spmm_carry_kernel<false>;
-            AGCN_KERNEL(k, cgrid, SPMM_THREADS, s, (const float *)p->carry, (const int *)p->carry_row, p->n_carry, prm.y, ldy,
+            AGCN_KERNEL(k, cgrid, SPMM_THREADS, s, (const float *)prm.carry, (const int *)p->carry_row, p->n_carry, prm.y, ldy,
                         prm.dim, activation, accumulate, prm.y_vec, prm.dim_store);
             AGCN_LAUNCH_CHECK("spmm_carry_kernel");
             p->launches_last_run++;
@@ -263,7 +283,7 @@ int spmm_run(agcn_spmm_plan *p, const int *d_indices, const float *d_vals, const
     bool x_vec = false;
     rc = spmm_prepare_x(p, d_x, ldx, dim, s, &x_use, &ldx_use, &x_vec);
     if (rc != AGCN_OK) return rc;
-    return spmm_run_prepared(p, d_indices, d_vals, x_use, ldx_use, x_vec, d_y, ldy, dim, s, activation, accumulate);
+    return spmm_run_prepared(p, d_indices, d_vals, x_use, ldx_use, x_vec, d_y, ldy, dim, s, activation, accumulate, SpmmLaunchPart());
 }
 
 }  // namespace agcn
@@ -307,122 +327,4 @@ extern "C" int agcn_spmm_plan_info(const agcn_spmm_plan *plan, int64_t *n_units,
     if (n_zero_rows) *n_zero_rows = plan->n_zero;
     if (launches_last_run) *launches_last_run = plan->launches_last_run;
     return AGCN_OK;
-}
-
-// ---------------------------------------------------------------------------
-// host-buffer calls
-// ---------------------------------------------------------------------------
-struct agcn_host_ctx {
-    cudaStream_t stream = nullptr;
-    void *buf[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};   // block4, idx, val, x, y
-    size_t cap[5] = {0, 0, 0, 0, 0};
-    agcn_spmm_plan *plan = nullptr;          // of the graph set by agcn_host_set_graph
-    int64_t n_rows = 0, n_cols = 0, nnz = 0;
-};
-
-namespace agcn {
-static int ctx_reserve(agcn_host_ctx *c, int which, size_t bytes)
-{
-    if (bytes <= c->cap[which]) return AGCN_OK;
-    if (c->buf[which] != nullptr) AGCN_CUDA(cudaFree(c->buf[which]));
-    c->buf[which] = nullptr; c->cap[which] = 0;
-    AGCN_CUDA(cudaMalloc(&c->buf[which], bytes));
-    c->cap[which] = bytes;
-    return AGCN_OK;
-}
-
-static int host_set_graph(agcn_host_ctx *ctx, const int *h_block4, int64_t n_blocks, const int *h_indices,
-                          const float *h_vals, int64_t n_rows, int64_t n_cols, int64_t nnz)
-{
-    AGCN_REQUIRE(ctx != nullptr, "agcn_host_set_graph: null context");
-    AGCN_REQUIRE(n_blocks >= 0 && (n_blocks == 0 || h_block4 != nullptr), "agcn_host_set_graph: null block4");
-    AGCN_REQUIRE(nnz >= 0 && (nnz == 0 || (h_indices != nullptr && h_vals != nullptr)), "agcn_host_set_graph: null indices or values");
-    AGCN_REQUIRE(n_rows > 0 && n_cols > 0, "agcn_host_set_graph: bad sizes");
-    plan_free(ctx->plan);
-    ctx->plan = nullptr;
-    const size_t bytes[3] = {(size_t)n_blocks * 16, (size_t)nnz * 4, (size_t)nnz * 4};
-    const void *src[3] = {h_block4, h_indices, h_vals};
-    for (int i = 0; i < 3; i++) {
-        int rc = ctx_reserve(ctx, i, bytes[i] > 0 ? bytes[i] : 16);
-        if (rc != AGCN_OK) return rc;
-        if (bytes[i] > 0) AGCN_CUDA(cudaMemcpyAsync(ctx->buf[i], src[i], bytes[i], cudaMemcpyHostToDevice, ctx->stream));
-    }
-    ctx->n_rows = n_rows; ctx->n_cols = n_cols; ctx->nnz = nnz;
-    return spmm_create(&ctx->plan, static_cast<const int *>(ctx->buf[0]), n_blocks, static_cast<const int *>(ctx->buf[1]),
-                       n_rows, n_cols, nnz, ctx->stream);
-}
-
-static int host_spmm(agcn_host_ctx *ctx, const float *h_x, float *h_y, int dim)
-{
-    AGCN_REQUIRE(ctx != nullptr && ctx->plan != nullptr, "agcn_host_spmm: no graph set (call agcn_host_set_graph first)");
-    AGCN_REQUIRE(h_x != nullptr && h_y != nullptr && dim >= 1, "agcn_host_spmm: null X or Y, or dim < 1");
-    const size_t xb = (size_t)ctx->n_cols * dim * 4, yb = (size_t)ctx->n_rows * dim * 4;
-    int rc = ctx_reserve(ctx, 3, xb);
-    if (rc == AGCN_OK) rc = ctx_reserve(ctx, 4, yb);
-    if (rc != AGCN_OK) return rc;
-    cudaStream_t s = ctx->stream;
-    AGCN_CUDA(cudaMemcpyAsync(ctx->buf[3], h_x, xb, cudaMemcpyHostToDevice, s));
-    rc = spmm_run(ctx->plan, static_cast<const int *>(ctx->buf[1]), static_cast<const float *>(ctx->buf[2]),
-                  static_cast<const float *>(ctx->buf[3]), dim, static_cast<float *>(ctx->buf[4]), dim, dim, s);
-    if (rc != AGCN_OK) {
-        cudaStreamSynchronize(s);
-        return rc;
-    }
-    AGCN_CUDA(cudaMemcpyAsync(h_y, ctx->buf[4], yb, cudaMemcpyDeviceToHost, s));
-    AGCN_CUDA(cudaStreamSynchronize(s));
-    return AGCN_OK;
-}
-}  // namespace agcn
-
-extern "C" int agcn_host_ctx_create(agcn_host_ctx **ctx)
-{
-    using namespace agcn;
-    clear_error();
-    AGCN_REQUIRE(ctx != nullptr, "agcn_host_ctx_create: null pointer");
-    *ctx = nullptr;
-    agcn_host_ctx *c = new (std::nothrow) agcn_host_ctx;
-    AGCN_REQUIRE(c != nullptr, "agcn_host_ctx_create: out of host memory");
-    cudaError_t e = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking);
-    if (e != cudaSuccess) {
-        set_error("agcn_host_ctx_create: cudaStreamCreate: %s", cudaGetErrorString(e));
-        delete c;
-        return AGCN_ERR_CUDA;
-    }
-    *ctx = c;
-    return AGCN_OK;
-}
-
-extern "C" int agcn_host_ctx_destroy(agcn_host_ctx *ctx)
-{
-    agcn::clear_error();
-    if (ctx == nullptr) return AGCN_OK;
-    agcn::plan_free(ctx->plan);
-    for (int i = 0; i < 5; i++) cudaFree(ctx->buf[i]);
-    if (ctx->stream) cudaStreamDestroy(ctx->stream);
-    delete ctx;
-    return AGCN_OK;
-}
-
-extern "C" int agcn_host_set_graph(agcn_host_ctx *ctx, const int32_t *h_block4, int64_t n_blocks,
-                                   const int32_t *h_indices, const float *h_vals,
-                                   int64_t n_rows, int64_t n_cols, int64_t nnz)
-{
-    agcn::clear_error();
-    return agcn::host_set_graph(ctx, h_block4, n_blocks, h_indices, h_vals, n_rows, n_cols, nnz);
-}
-
-extern "C" int agcn_host_spmm(agcn_host_ctx *ctx, const float *h_x, float *h_y, int dim)
-{
-    agcn::clear_error();
-    return agcn::host_spmm(ctx, h_x, h_y, dim);
-}
-
-extern "C" int agcn_spmm_host(agcn_host_ctx *ctx, const int32_t *h_block4, int64_t n_blocks,
-                              const int32_t *h_indices, const float *h_vals, const float *h_x, float *h_y,
-                              int64_t n_rows, int64_t n_cols, int64_t nnz, int dim)
-{
-    agcn::clear_error();
-    int rc = agcn::host_set_graph(ctx, h_block4, n_blocks, h_indices, h_vals, n_rows, n_cols, nnz);
-    if (rc != AGCN_OK) return rc;
-    return agcn::host_spmm(ctx, h_x, h_y, dim);
 }

@@ -147,7 +147,7 @@ static int tiled_run(agcn_spmm_tiled *t, int k0, int k1, const float *d_x, int64
         // the first range stores Y (and zero-fills rows it does not cover), later ranges add to it in
         // range order; the activation is applied by the last range, to every row
         rc = spmm_run_prepared(p, t->idx + off, t->val + off, x_use, ldx_use, x_vec, d_y, ldy, dim, s,
-                               k == t->n_ranges - 1 ? activation : 0, k > 0 ? 1 : 0);
+                               k == t->n_ranges - 1 ? activation : 0, k > 0 ? 1 : 0, SpmmLaunchPart());
         if (rc != AGCN_OK) return rc;
         t->launches_last_run += p->launches_last_run;
     }
