@@ -10,11 +10,13 @@ One step = one pass of the SpMM over the workload's dense widths (config 2: dim 
             from pinned host memory and Y comes back, every step, inside the timed region
   roofline  compulsory HBM bytes of the widest product / its CUDA-event time, against the
             measured copy bandwidth of this pool's B200s
-  cpu_baseline  the CPU restatement of the reference path (oracle) on a bounded row sample
+  cpu_baseline  the CPU restatement of the reference path (oracle) on a bounded row sample, with the
+            Python partition walk and scipy's single-threaded csr @ dense beside it
 
 `--impl reference` times that CPU path alone, with all host threads, on the same workload.
-Under torchrun with N > 1 the matrix is row-sharded by nonzeros and every step all-gathers
-the dense operand (strong scaling: the total work is fixed).
+Under torchrun with N > 1 the matrix is row-sharded (two row ranges per rank: equal rows and equal
+nonzeros) and every step all-gathers the dense operand over NCCL inside the library (strong
+scaling: the total work is fixed).
 """
 from __future__ import annotations
 
@@ -55,7 +57,9 @@ GCN_WORKLOADS = ("cfg5", "cfg5-5m", "cfg5-1m", "cfg5-small")
 WORKLOADS["replicas"] = (0, 1.0, (64,))
 METRIC, UNIT = "spmm_gflops", "GFLOP/s"
 FALLBACK_HBM_GBS = 6650.0
-NCU_TRAFFIC_BYTES = {("cfg2", 128): 4.070e9}      # (workload, dim) -> DRAM bytes per product, from ncu
+# (workload, dim, kernel variant) -> dram__bytes_read + dram__bytes_write per product, from the ncu captures
+# summarised under profiles/ (same command as the default run)
+NCU_TRAFFIC_BYTES = {("cfg2", 128, "two 64-column passes"): 4.070e9}
 
 
 def hbm_peak():
@@ -151,6 +155,23 @@ def build_workload(name, dev):
     return g, ip, ix, v, dims
 
 
+def build_workload_reference(name):
+    """The same degree-ordered matrix for the reference arm, without loading this repository's
+    library: the generator is torch arithmetic (run on the GPU when there is one, only to save
+    minutes of CPU sorting) and the ordering is the oracle's (numpy)."""
+    import torch
+    from accelgcn import synth
+    from oracle import oracle
+    cfg, scale, dims = WORKLOADS[name]
+    g = synth.make_config(cfg, "cuda:0" if torch.cuda.is_available() else "cpu", scale)
+    ip_h, ix_h, v_h = g.indptr.cpu().numpy(), g.indices.cpu().numpy(), g.vals.cpu().numpy()
+    info = dict(g.info)
+    n = g.n
+    del g
+    _perm, ip_h, ix_h, v_h = oracle.degree_sort(ip_h, ix_h, v_h, True)
+    return n, info, ip_h, ix_h, v_h, dims
+
+
 def row_sample(ip_h, ix_h, v_h, stride):
     """Every stride-th row of a host CSR matrix (degree-ordered, so a strided sample keeps the degree mix)."""
     if stride <= 1:
@@ -188,22 +209,52 @@ def cpu_spmm_rate(ip_h, ix_h, v_h, xs, budget_s):
     return 2.0 * len(si) * dsum / dt / 1e9, dt, desc, stride
 
 
+def cpu_reference_extras(ip_h, ix_h, v_h, xs, stride, budget_s=6.0):
+    """What the reference itself runs on the CPU for this path, timed on bounded samples: the
+    partition walk of block_level_partition.py:48-103 (pure Python, one core -- the restatement in
+    oracle.partition_py; the script itself does not travel to the GPU box) and scipy's csr @ dense
+    in fp32 (single-threaded), the product its results are checked against."""
+    import scipy.sparse as sp
+    from oracle import oracle
+    n = len(ip_h) - 1
+    rows = min(n, 400_000)
+    t0 = time.perf_counter()
+    b4 = oracle.partition_py(np.concatenate([[0], np.cumsum(np.diff(ip_h[: rows + 1].astype(np.int64)))]))
+    dt_part = time.perf_counter() - t0
+    sp_ip, sp_ix, sp_v = row_sample(ip_h, ix_h, v_h, max(stride, 1))
+    # scipy is ~50x slower than the threaded port: shrink the sample to stay within the budget
+    keep = max(1, int(len(sp_ip) - 1))
+    a = sp.csr_matrix((sp_v, sp_ix, sp_ip), shape=(keep, xs[0].shape[0]))
+    probe_rows = max(1, keep // 64)
+    t0 = time.perf_counter()
+    a[:probe_rows] @ xs[0]
+    est = (time.perf_counter() - t0) * 64 * sum(x.shape[1] for x in xs) / xs[0].shape[1]
+    frac = min(1.0, budget_s / max(est, 1e-6))
+    a = a[: max(1, int(keep * frac))]
+    t0 = time.perf_counter()
+    for x in xs:
+        a @ x
+    dt_sp = time.perf_counter() - t0
+    return {"partition_walk": {"rows_per_s": rows / dt_part, "rows": rows, "tuples": int(len(b4)), "seconds": dt_part,
+                               "cores": 1, "what": "pure-Python walk of block_level_partition.py:48-103 (oracle.partition_py) "
+                                                   "on the first rows of the workload's row pointers"},
+            "scipy_csr_dense": {"value": 2.0 * a.nnz * sum(x.shape[1] for x in xs) / dt_sp / 1e9, "unit": UNIT, "cores": 1,
+                                "seconds": dt_sp, "sample": f"{a.shape[0]} rows / {a.nnz} nonzeros of the port's sample, all widths, fp32"}}
+
+
 # ----------------------------------------------------------------------------------------
 def reference_arm(args, rank, world):
     """The reference's CPU path for the SpMM (its only CPU code is the Python partitioner; the
-    product it is checked against is CSR x dense), restated in C with OpenMP in oracle/."""
+    product it is checked against is CSR x dense), restated in C with OpenMP in oracle/.  Nothing
+    of this repository's library is loaded in this arm."""
     if rank != 0:
         return
-    import torch
     from oracle import oracle
-    dev = "cuda:0" if torch.cuda.is_available() else "cpu"
-    g, ip, ix, v, dims = build_workload(args.workload, dev)
-    n, nnz = g.n, int(ix.numel())
-    ip_h, ix_h, v_h = ip.cpu().numpy(), ix.cpu().numpy(), v.cpu().numpy()
-    n_blocks = int(len(oracle.partition(ip_h)))
     from accelgcn import synth
-    xs = [synth.features(n, d, g.info["seed"], "cpu").numpy() for d in dims]
-    del g, ip, ix, v
+    n, info, ip_h, ix_h, v_h, dims = build_workload_reference(args.workload)
+    nnz = len(ix_h)
+    n_blocks = int(len(oracle.partition(ip_h)))
+    xs = [synth.features(n, d, info["seed"], "cpu").numpy() for d in dims]
     dsum = sum(dims)
     per_step = min(2.0, 150.0 / max(args.steps + args.warmup, 1))
     _rate, _dt, desc, stride = cpu_spmm_rate(ip_h, ix_h, v_h, xs, per_step)
@@ -223,13 +274,31 @@ def reference_arm(args, rank, world):
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": workload_description(args.workload, info, n, nnz, n_blocks, dims),
             "cpu_baseline": {"value": gflops, "unit": UNIT, "cores": oracle.num_threads(), "kind": "port",
-                             "sample": "each step: " + desc},
+                             "sample": "each step: " + desc,
+                             "reference_cpu_path": cpu_reference_extras(ip_h, ix_h, v_h, xs, stride)},
             "e2e": {"value": gflops, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line), flush=True)
 
 
 # ----------------------------------------------------------------------------------------
+def gather_peaks(dims):
+    """Measured ceiling of the gather itself: GB/s of whole-row reads from an L2-resident table (32 MB)
+    with the SpMM's access shape, per row width (agcn_probe_gather_bandwidth)."""
+    import ctypes
+    from accelgcn import _lib
+    lib = _lib.load()
+    out = {}
+    for d in sorted(set(dims)):
+        if d not in (32, 64, 128):
+            continue
+        gbs = ctypes.c_double(0.0)
+        rows = (32 << 20) // (4 * d)
+        _lib.check(lib.agcn_probe_gather_bandwidth(rows, d, (2 << 30) // (4 * d), 5, ctypes.byref(gbs)))
+        out[d] = gbs.value
+    return out
+
+
 def ours(args, rank, world, local_rank):
     import torch
     import torch.distributed as dist
@@ -249,43 +318,64 @@ def ours(args, rank, world, local_rank):
 
     g, ip, ix, v, dims = build_workload(args.workload, dev)
     n, nnz = g.n, int(ix.numel())
-    shard = sharded.ShardedSpmm(ip, ix, v, rank, world)
-    ip_full_h = ip.cpu().numpy() if rank == 0 else None
-    r0, r1 = shard.row_range
-    n_blocks_local = int(shard.block4.shape[0])
+    assert len(dims) <= 4, "one exchange slot per product of a step"
+    # one block of A per rank (two row ranges: equal rows and equal nonzeros); the dense operands and
+    # results are block rows.  On one GPU the block is the whole matrix and nothing is exchanged.
+    shard = sharded.ShardedSpmm(ip, ix, v, rank, world, exchange_slices=args.slices if world > 1 else 1)
+    per = shard.rows_per_block
+    n_blocks_local = int(shard.n_blocks)
     nb = torch.tensor([n_blocks_local], dtype=torch.int64, device=dev)
     if world > 1:
         dist.all_reduce(nb)
     n_blocks = int(nb.item())
-    # the dense operand is block-distributed evenly over the ranks (one balanced all-gather per
-    # product); on one GPU the block is the whole operand
-    xs = {d: shard.even_block(synth.features(n, d, g.info["seed"], dev)) for d in dims}
-    ys = {d: torch.empty((r1 - r0, d), dtype=torch.float32, device=dev) for d in dims}
+    xs = {d: shard.to_block(synth.features(n, d, g.info["seed"], dev)) for d in dims}
+    ys = {d: torch.empty((per, d), dtype=torch.float32, device=dev) for d in dims}
+    # single GPU: a product whose X does not stay in L2 runs column-tiled (A regrouped by column range)
+    tiled = {}
+    if world == 1 and args.tiled != "off":
+        lib = _lib.load()
+        for d in dims:
+            k = lib.agcn_spmm_tiled_suggest(n, n, nnz, d)
+            if k > 1:
+                tiled[d] = spmm_mod.TiledSpmmPlan(ip, ix, v, n, n, dim=d)
+    ip_full_h = ip.cpu().numpy() if rank == 0 else None
     if world > 1:
         del ip, ix, v
     torch.cuda.empty_cache()
 
-    launches = [0]
-
     def step(record=None):
-        # the products of a step are independent: all their all-gathers are started first (they run
-        # on the process group's stream), and each SpMM waits only for its own operand
-        pending = [shard.gather_even_async(xs[d]) for d in dims]
-        launches[0] = 0
+        # the products of a step are independent: all their exchanges are started first (on the
+        # library's communication stream), and each SpMM waits only for its own operand, slice by slice
+        if world > 1:
+            for di, d in enumerate(dims):
+                shard.gather_begin(xs[d], slot=di)
         for di, d in enumerate(dims):
             if record is not None:
                 record[di][0].record()
-            x_full, work = pending[di]
-            if work is not None:
-                work.wait()
-            shard.step(None, ys[d], x_gathered=x_full)
-            launches[0] += shard.plan.info()["launches_last_run"]
+            if d in tiled:
+                tiled[d].run(xs[d], ys[d])
+            elif world > 1:
+                shard.multiply(ys[d], slot=di)
+            else:
+                shard.step(xs[d], ys[d])
             if record is not None:
                 record[di][1].record()
 
+    def count_launches():
+        total = 0
+        for di, d in enumerate(dims):
+            if d in tiled:
+                tiled[d].run(xs[d], ys[d]); total += tiled[d].info()["launches_last_run"]
+            elif world > 1:
+                shard.gather_begin(xs[d], slot=di); shard.multiply(ys[d], slot=di); total += shard.info()["launches_last_step"]
+            else:
+                shard.step(xs[d], ys[d]); total += shard.info()["launches_last_step"]
+        return total
+
     for _ in range(max(args.warmup, 3)):
         step()
-    launches_per_step = launches[0]
+    barrier()
+    launches_per_step = count_launches()
     barrier()
 
     uuid = str(getattr(torch.cuda.get_device_properties(dev), "uuid", ""))
@@ -317,57 +407,96 @@ def ours(args, rank, world, local_rank):
     flops_step = 2.0 * nnz * sum(dims)
     value = flops_step * args.steps / (total_ms / 1e3) / 1e9
 
+    # where the time goes on several GPUs: the same products with nothing exchanged (the operand of
+    # the previous step is still in the slots), and the exchanges alone
+    multi = None
+    if world > 1:
+        def timed_loop(fn, reps=10):
+            fn(); barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(reps):
+                fn()
+            b.record(); barrier()
+            tt = torch.tensor([a.elapsed_time(b) / reps], dtype=torch.float64, device=dev)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            return float(tt.item())
+
+        def only_products():
+            for di, d in enumerate(dims):
+                shard.multiply(ys[d], slot=di)
+
+        compute_ms = timed_loop(only_products)
+        nnz_local = torch.tensor([shard.local_nnz], dtype=torch.float64, device=dev)
+        nnz_max = nnz_local.clone(); dist.all_reduce(nnz_max, op=dist.ReduceOp.MAX)
+        multi = {"step_ms": total_ms / args.steps, "products_without_exchange_ms": compute_ms,
+                 "exchange_and_wait_ms": total_ms / args.steps - compute_ms,
+                 "exchange_slices": shard.slices,
+                 "rows_per_block": per, "max_local_nnz_over_mean": float(nnz_max.item()) * world / nnz,
+                 "exchanged_bytes_in_per_rank_per_step": 4 * sum(dims) * per * (world - 1),
+                 "limiting_phase": "products" if compute_ms > 0.5 * total_ms / args.steps else "exchange"}
+
     if args.kernel_only:
         # profiling mode: the resident-data loop only (no end-to-end, CPU or reference legs)
         if rank == 0:
             print(json.dumps({"metric": METRIC, "value": value, "unit": UNIT, "steps": args.steps,
-                              "ms_per_step": total_ms / args.steps, "per_dim_ms": per_dim_ms, "kernel_only": True}))
+                              "ms_per_step": total_ms / args.steps, "per_dim_ms": per_dim_ms, "kernel_only": True,
+                              "tiled_dims": sorted(tiled), "multi_gpu": multi}))
         if world > 1:
             dist.destroy_process_group()
         return
 
-    # ---- end to end through the host-buffer C-ABI call, pinned host memory -------------------
+    # ---- end to end through the host-buffer C-ABI calls, pinned host memory --------------------
+    # every rank's inputs are its block of A (.block4, renamed column ids, values: rebuilt on the host
+    # from the same layout) and the whole X; its outputs are its rows of Y
     host = spmm_mod.HostSpmm()
-    hb = {"b4": shard.block4.cpu().pin_memory(), "ix": shard.indices.cpu().pin_memory(),
-          "v": shard.vals.cpu().pin_memory()}
-    hx, hy = {}, {}
-    for d in dims:
-        full = synth.features(n, d, g.info["seed"], dev)
-        hx[d] = full.cpu().pin_memory()
-        hy[d] = torch.empty((r1 - r0, d), dtype=torch.float32).pin_memory()
-        del full
-    e2e_steps = max(1, min(args.steps, 5))
+    n_rows_host, n_cols_host = n, n
+    if world == 1:
+        from accelgcn import partition
+        hb = {"b4": partition.block_level_partition_device(ip).cpu().pin_memory(), "ix": ix.cpu().pin_memory(),
+              "v": v.cpu().pin_memory()}
+        hx = {d: xs[d].cpu().pin_memory() for d in dims}
+    e2e = None
+    if world == 1:
+        hy = {d: torch.empty((n_rows_host, d), dtype=torch.float32).pin_memory() for d in dims}
+        e2e_steps = max(1, min(args.steps, 5))
 
-    n_cols_host = int(hx[dims[0]].shape[0])
+        def e2e_step(with_graph=True):
+            # every input of the step crosses PCIe once: with_graph -> .block4, column ids and values too
+            if with_graph:
+                host.step_batch(hb["b4"], hb["ix"], hb["v"], [hx[d] for d in dims], n_rows_host, outs=[hy[d] for d in dims])
+            else:
+                host.run_batch([hx[d] for d in dims], outs=[hy[d] for d in dims])
 
-    def e2e_step(with_graph=True):
-        # every input of the step crosses PCIe once: the graph (.block4, column ids, values), then
-        # per width X up and Y down
-        if with_graph:
-            host.set_graph(hb["b4"], hb["ix"], hb["v"], r1 - r0, n_cols_host)
-        for d in dims:
-            host.run(hx[d], out=hy[d])
-
-    def timed(fn, reps):
-        fn()
-        barrier()
-        t0 = time.perf_counter()
-        for _ in range(reps):
+        def timed(fn, reps):
             fn()
-        barrier()
-        dt = torch.tensor([time.perf_counter() - t0], dtype=torch.float64, device=dev)
-        if world > 1:
-            dist.all_reduce(dt, op=dist.ReduceOp.MAX)
-        return float(dt.item())
+            barrier()
+            t0 = time.perf_counter()
+            for _ in range(reps):
+                fn()
+            barrier()
+            return time.perf_counter() - t0
 
-    e2e_s = timed(e2e_step, e2e_steps)
-    e2e_value = flops_step * e2e_steps / e2e_s / 1e9
-    resident_s = timed(lambda: e2e_step(False), e2e_steps)           # graph uploaded once, at set-up
-    graph_bytes = 16 * n_blocks_local + 8 * int(shard.indices.numel())
-    h2d = graph_bytes + sum(4 * d * n_cols_host for d in dims)
-    d2h = sum(4 * d * (r1 - r0) for d in dims)
-    e2e_ok = bool(torch.equal(hy[dims[-1]], ys[dims[-1]].cpu()))     # same bits as the resident run
+        e2e_s = timed(e2e_step, e2e_steps)
+        e2e_ok = all(bool(torch.equal(hy[d], ys[d].cpu())) for d in dims if d not in tiled)
+        resident_s = timed(lambda: e2e_step(False), e2e_steps)           # graph uploaded once, at set-up
+        e2e_ok = e2e_ok and all(bool(torch.equal(hy[d], ys[d].cpu())) for d in dims if d not in tiled)
+        graph_bytes = 16 * int(hb["b4"].shape[0]) + 8 * nnz
+        h2d = graph_bytes + sum(4 * d * n_cols_host for d in dims)
+        d2h = sum(4 * d * n_rows_host for d in dims)
+        e2e = {"value": flops_step * e2e_steps / e2e_s / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+               "steps": e2e_steps, "ms_per_step": e2e_s / e2e_steps * 1e3,
+               "pcie_gbs_up": h2d / (e2e_s / e2e_steps) / 1e9,
+               "call": "agcn_spmm_host_batch: graph and X up, Y down, A multiplied range by range as it arrives",
+               "bit_identical_to_resident_run": e2e_ok,
+               "graph_resident": {"value": flops_step * e2e_steps / resident_s / 1e9, "unit": UNIT,
+                                  "ms_per_step": resident_s / e2e_steps * 1e3,
+                                  "h2d_bytes_per_step": h2d - graph_bytes, "d2h_bytes_per_step": d2h,
+                                  "call": "agcn_host_spmm_batch",
+                                  "note": "graph uploaded once at set-up (SPMM_BASE constructor), X and Y cross PCIe every step"}}
     host.close()
+    if world > 1:
+        e2e = e2e_sharded(args, shard, xs, ys, dims, dev, world, barrier, flops_step)
 
     if rank != 0:
         if world > 1:
@@ -376,54 +505,105 @@ def ours(args, rank, world, local_rank):
 
     peak, peak_src = hbm_peak()
     props = torch.cuda.get_device_properties(dev)
+    sm_mhz = clocks["sm_mhz"] or clocks["sm_max_mhz"] or 1965.0
+    fp32_peak = props.multi_processor_count * 128 * 2 * sm_mhz * 1e6
+    l2_peaks = gather_peaks(dims) if world == 1 else {}
     per_dim = []
     for d, ms in zip(dims, per_dim_ms):
         b = min_bytes(nnz, n_blocks, n, n, d)
-        per_dim.append({"dim": d, "ms": ms, "gflops": 2.0 * nnz * d / ms / 1e6, "hbm_gbs": b / ms / 1e6,
-                        "hbm_frac": b / ms / 1e6 / peak,
-                        "gather_gbs_l2_inclusive": (nnz * (8 + 4 * d) + 4 * d * n + 16 * n_blocks) / ms / 1e6})
+        t_hbm, t_fp32 = b / (peak * 1e9) * 1e3, 2.0 * nnz * d / fp32_peak * 1e3
+        gather_gbs = (nnz * (8 + 4 * d) + 4 * d * n + 16 * n_blocks) / ms / 1e6
+        row = {"dim": d, "ms": ms, "gflops": 2.0 * nnz * d / ms / 1e6, "hbm_gbs": b / ms / 1e6,
+               "hbm_frac": b / ms / 1e6 / peak, "t_bound_ms": max(t_hbm, t_fp32),
+               "bound_term": "hbm" if t_hbm >= t_fp32 else "fp32", "frac_of_t_bound": max(t_hbm, t_fp32) / ms,
+               "gather_gbs_l2_inclusive": gather_gbs, "kernel": "column-tiled" if d in tiled else "one launch set"}
+        if d in l2_peaks:
+            row["l2_gather_peak_gbs"] = l2_peaks[d]
+            row["gather_frac_of_measured_l2_peak"] = gather_gbs / l2_peaks[d]
+        per_dim.append(row)
     top = max(per_dim, key=lambda r: r["ms"])
-    fp32_peak = props.multi_processor_count * 128 * 2 * (clocks["sm_mhz"] or clocks["sm_max_mhz"] or 1965.0) * 1e6
-    # dram__bytes_read + dram__bytes_write of that product, from an ncu capture of this same command
-    # (summarised under profiles/; known for the default workload on one GPU only)
-    traffic = NCU_TRAFFIC_BYTES.get((args.workload, top["dim"])) if world == 1 else None
+    variant = "column-tiled" if top["dim"] in tiled else ("two 64-column passes" if top["dim"] > 64 else "one pass")
+    traffic = NCU_TRAFFIC_BYTES.get((args.workload, top["dim"], variant)) if world == 1 else None
+    # `bound`/`achieved`/`frac` follow the contract: compulsory HBM bytes per launch over the CUDA-event
+    # time against the measured copy bandwidth.  Which resource really binds is named beside it.
     roofline = {"bound": "hbm", "achieved": top["hbm_gbs"], "peak": peak, "unit": "GB/s",
-                "frac": top["hbm_frac"], "traffic": traffic, "kernel": f"spmm_units_kernel dim={top['dim']}",
+                "frac": top["hbm_frac"], "traffic": traffic, "kernel": f"spmm_units_kernel dim={top['dim']} ({variant})",
                 "peak_source": peak_src,
                 "algorithmic_bytes_per_launch": min_bytes(nnz, n_blocks, n, n, top["dim"]),
-                "fp32_frac_at_sampled_clock": 2.0 * nnz * top["dim"] / (top["ms"] / 1e3) / fp32_peak}
+                "binding_term_of_max_hbm_fp32": top["bound_term"], "frac_of_t_bound": top["frac_of_t_bound"],
+                "fp32_frac_at_sampled_clock": 2.0 * nnz * top["dim"] / (top["ms"] / 1e3) / fp32_peak,
+                "l2_gather_peak_gbs": top.get("l2_gather_peak_gbs"),
+                "gather_frac": top.get("gather_frac_of_measured_l2_peak"),
+                "note": "the gather moves nnz*4*dim bytes of X through L2 for 4*dim*N bytes from HBM; "
+                        "gather_frac = L2-inclusive bytes per second over the measured L2 gather rate of this GPU"}
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": total_ms / args.steps, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": workload_description(args.workload, g.info, n, nnz, n_blocks, dims),
-            "roofline": roofline, "per_dim": per_dim, "clocks": clocks,
-            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "steps": e2e_steps, "ms_per_step": e2e_s / e2e_steps * 1e3,
-                    "pcie_gbs": (h2d + d2h) / (e2e_s / e2e_steps) / 1e9,
-                    "bit_identical_to_resident_run": e2e_ok,
-                    "graph_resident": {"value": flops_step * e2e_steps / resident_s / 1e9, "unit": UNIT,
-                                       "h2d_bytes_per_step": h2d - graph_bytes, "d2h_bytes_per_step": d2h,
-                                       "note": "graph uploaded once at set-up (SPMM_BASE constructor), X and Y cross PCIe every step"}},
+            "roofline": roofline, "per_dim": per_dim, "clocks": clocks, "e2e": e2e,
             "gpu_launches": launches_per_step * args.steps,
-            "plan": shard.plan.info(), "preprocess_ms": g.info.get("preprocess_ms")}
+            "plan": shard.info(), "preprocess_ms": g.info.get("preprocess_ms")}
+    if multi is not None:
+        line["multi_gpu"] = multi
 
     if world == 1:
         ip_h, ix_h, v_h = ip_full_h, ix.cpu().numpy(), v.cpu().numpy()
         xs_h = [xs[d].cpu().numpy() for d in dims]
         if not args.no_ref_gpu:
-            line["reference_gpu"] = reference_gpu_kernels(shard.block4.cpu().numpy(), ip_h, ix_h, v_h, xs_h, dims, nnz)
+            from accelgcn import partition
+            b4_h = partition.block_level_partition_device(ip).cpu().numpy()
+            line["reference_gpu"] = reference_gpu_kernels(b4_h, ip_h, ix_h, v_h, xs_h, dims, nnz)
         from oracle import oracle
-        gf, dt, desc, _ = cpu_spmm_rate(ip_h, ix_h, v_h, xs_h, args.cpu_seconds)
+        gf, dt, desc, stride = cpu_spmm_rate(ip_h, ix_h, v_h, xs_h, args.cpu_seconds)
         line["cpu_baseline"] = {"value": gf, "unit": UNIT, "cores": oracle.num_threads(), "kind": "port",
-                                "sample": desc, "seconds": dt}
+                                "sample": desc, "seconds": dt,
+                                "reference_cpu_path": cpu_reference_extras(ip_h, ix_h, v_h, xs_h, stride)}
     else:
         dist.destroy_process_group()
     print(json.dumps(line), flush=True)
 
 
+def e2e_sharded(args, shard, xs, ys, dims, dev, world, barrier, flops_step):
+    """End to end on several GPUs: every rank's block rows of X go up from pinned host memory, the
+    step (exchange + products) runs, its block rows of Y come down -- all inside the timed region."""
+    import torch
+    import torch.distributed as dist
+    hx = {d: xs[d].cpu().pin_memory() for d in dims}
+    hy = {d: torch.empty(tuple(ys[d].shape), dtype=torch.float32).pin_memory() for d in dims}
+    xd = {d: torch.empty_like(xs[d]) for d in dims}
+
+    def step():
+        for d in dims:
+            xd[d].copy_(hx[d], non_blocking=True)
+        for di, d in enumerate(dims):
+            shard.gather_begin(xd[d], slot=di)
+        for di, d in enumerate(dims):
+            shard.multiply(ys[d], slot=di)
+            hy[d].copy_(ys[d], non_blocking=True)
+        torch.cuda.synchronize(dev)
+
+    reps = max(1, min(args.steps, 5))
+    step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        step()
+    barrier()
+    dt = torch.tensor([time.perf_counter() - t0], dtype=torch.float64, device=dev)
+    dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+    same = all(bool(torch.equal(hy[d], ys[d].cpu())) for d in dims)
+    per = shard.rows_per_block
+    return {"value": flops_step * reps / float(dt.item()) / 1e9, "unit": UNIT,
+            "h2d_bytes_per_step": sum(4 * d * per for d in dims), "d2h_bytes_per_step": sum(4 * d * per for d in dims),
+            "steps": reps, "ms_per_step": float(dt.item()) / reps * 1e3, "bit_identical_to_resident_run": same,
+            "call": "per rank: block rows of X up, agcn_dist_gather_begin + agcn_dist_spmm_gathered, block rows of Y down "
+                    "(each rank's block of A is resident)"}
+
+
 def ours_gcn(args, rank, world, local_rank):
-    """Two-layer GCN forward on the row-sharded operator (configuration 5).  One step = one forward:
-    per layer a TF32 GEMM on the owned rows, an all-gather of the result, the SpMM with fused ReLU."""
+    """Two-layer GCN forward on the row-sharded operator (configuration 5) through agcn_gcn2_forward_*.
+    One step = one forward: per layer a TF32 GEMM on the owned rows, the all-gather of the result, the
+    SpMM with fused ReLU."""
     import torch
     import torch.distributed as dist
     from accelgcn import synth, sharded, gcn, _lib
@@ -443,71 +623,81 @@ def ours_gcn(args, rank, world, local_rank):
     g, ip, ix, v, _dims = build_workload(args.workload, dev)
     n, nnz, seed, info = g.n, int(ix.numel()), g.info["seed"], dict(g.info)
     del g
-    shard = sharded.ShardedSpmm(ip, ix, v, rank, world)
+    shard = sharded.ShardedSpmm(ip, ix, v, rank, world, exchange_slices=args.slices if world > 1 else 1)
     ip_h = ip.cpu().numpy() if rank == 0 and world == 1 else None
-    ix_keep, v_keep = (ix, v) if world == 1 else (None, None)
+    ip_keep, ix_keep, v_keep = (ip, ix, v) if world == 1 else (None, None, None)
     del ip, ix, v
     torch.cuda.empty_cache()
-    r0, r1 = shard.row_range
-    nb = torch.tensor([int(shard.block4.shape[0])], dtype=torch.int64, device=dev)
+    per = shard.rows_per_block
+    nb = torch.tensor([int(shard.n_blocks)], dtype=torch.int64, device=dev)
     if world > 1:
         dist.all_reduce(nb)
     n_blocks = int(nb.item())
-    # this rank's rows of X, generated in slabs (the generator addresses elements by index)
-    x_local = torch.empty((r1 - r0, 128), dtype=torch.float32, device=dev)
-    slab = 4_000_000
-    for a in range(r0, r1, slab):
-        b = min(r1, a + slab)
-        x_local[a - r0:b - r0] = synth.uniform_f32(seed, 7, a * 128, (b - a) * 128, -1.0, 1.0, dev).reshape(b - a, 128)
+    # this rank's block rows of X, generated row by row (the generator addresses elements by index)
+    def x_rows(rows):
+        out = torch.empty((rows.numel(), 128), dtype=torch.float32, device=dev)
+        for a in range(0, rows.numel(), 2_000_000):
+            r = rows[a:a + 2_000_000]
+            base = (r * 128).unsqueeze(1) + torch.arange(128, device=dev, dtype=torch.int64)
+            out[a:a + r.numel()] = synth.uniform_f32_at(seed, 7, base.reshape(-1), -1.0, 1.0).reshape(-1, 128)
+        return out
+    x_block = shard.to_block(x_rows)
     w1, w2 = synth.glorot(128, 128, seed, 8, dev), synth.glorot(128, 128, seed, 9, dev)
     fwd = gcn.GcnForward(shard, [w1, w2])
+    out = torch.empty_like(x_block)
 
     for _ in range(max(args.warmup, 3)):
-        fwd.forward(x_local)
+        fwd.forward(x_block, out=out)
     barrier()
+    fwd.status()
     uuid = str(getattr(torch.cuda.get_device_properties(dev), "uuid", ""))
     sampler = ClockSampler(uuid)
-    timings = []
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    parts_sum = np.zeros(6)
     barrier()
     e0.record()
     for _ in range(args.steps):
-        out = fwd.forward(x_local, timings)
+        fwd.forward(x_block, out=out)
     e1.record()
     barrier()
+    parts_sum += np.asarray(fwd.status(timings=True)).reshape(-1)       # the last forward's split
     t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     for _ in range(int(max(0.0, 1500.0 - float(t.item())) / max(float(t.item()) / args.steps, 1e-3))):
-        fwd.forward(x_local)           # same count on every rank (it comes from the reduced time)
+        fwd.forward(x_block, out=out)           # same count on every rank (it comes from the reduced time)
     torch.cuda.synchronize(dev)
     clocks = sampler.stop()
-    parts = torch.tensor([np.mean([ev[i].elapsed_time(ev[i + 1]) for ev in timings]) for i in range(3)],
-                         dtype=torch.float64, device=dev)          # per layer: gemm, all-gather, spmm
+    parts = torch.tensor(parts_sum, dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(parts, op=dist.ReduceOp.MAX)
     total_ms = float(t.item())
-    gemm_ms, gather_ms, spmm_ms = parts.tolist()
+    p = parts.tolist()
+    gemm_ms, gather_ms, spmm_ms = (p[0] + p[3]) / 2, (p[1] + p[4]) / 2, (p[2] + p[5]) / 2
     flops_step = 2 * (2.0 * nnz * 128 + 2.0 * n * 128 * 128)
     value = flops_step * args.steps / (total_ms / 1e3) / 1e9
+    per_layer = {"gemm": gemm_ms, "wait_for_first_exchanged_slice": gather_ms, "spmm_relu_incl_later_slices": spmm_ms,
+                 "exchange_slices": shard.slices,
+                 "exchanged_bytes_in_per_rank_per_layer": 4 * 128 * per * (world - 1),
+                 "limiting_phase": max((("gemm", gemm_ms), ("exchange", gather_ms), ("spmm", spmm_ms)), key=lambda kv: kv[1])[0]}
 
     if args.kernel_only:
         if rank == 0:
             print(json.dumps({"metric": METRIC, "value": value, "unit": UNIT, "steps": args.steps,
-                              "ms_per_step": total_ms / args.steps, "kernel_only": True,
-                              "per_layer_ms": {"gemm": gemm_ms, "all_gather": gather_ms, "spmm_relu": spmm_ms}}))
+                              "ms_per_step": total_ms / args.steps, "kernel_only": True, "per_layer_ms": per_layer}))
         if world > 1:
             dist.destroy_process_group()
         return
 
-    # end to end: X rows up from pinned host memory, forward, output rows down
-    hx = x_local.cpu().pin_memory()
-    hy = torch.empty((r1 - r0, 128), dtype=torch.float32).pin_memory()
-    xd = torch.empty_like(x_local)
+    # end to end: block rows of X up from pinned host memory, forward, block rows of the output down
+    hx = x_block.cpu().pin_memory()
+    hy = torch.empty((per, 128), dtype=torch.float32).pin_memory()
+    xd = torch.empty_like(x_block)
+    out2 = torch.empty_like(x_block)
 
     def e2e_step():
         xd.copy_(hx, non_blocking=True)
-        hy.copy_(fwd.forward(xd), non_blocking=True)
+        hy.copy_(fwd.forward(xd, out=out2), non_blocking=True)
         torch.cuda.synchronize(dev)
 
     e2e_steps = max(1, min(args.steps, 3))
@@ -522,23 +712,23 @@ def ours_gcn(args, rank, world, local_rank):
         dist.all_reduce(e2e_s, op=dist.ReduceOp.MAX)
     e2e_value = flops_step * e2e_steps / float(e2e_s.item()) / 1e9
     same = bool(torch.equal(hy, out.cpu()))
+    sampled = gcn_sampled_check(ip_keep, ix_keep, v_keep, x_rows, w1, w2, out, dev) if world == 1 else None
     if rank != 0:
         dist.destroy_process_group()
         return
 
     peak, peak_src = hbm_peak()
-    n_loc = r1 - r0
-    gemm_bytes = 2 * 4 * 128 * n_loc + 4 * 128 * 128                       # H read + Z written (+ W)
-    spmm_bytes = min_bytes(int(shard.indices.numel()), int(shard.block4.shape[0]), n_loc, n, 128)
+    gemm_bytes = 2 * 4 * 128 * per + 4 * 128 * 128                       # H read + Z written (+ W)
+    spmm_bytes = min_bytes(int(shard.local_nnz), int(shard.n_blocks), per, shard.n_gathered, 128)
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": total_ms / args.steps, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32 (SpMM), tf32 multiply / f32 accumulate (X*W)",
             "data": "synthetic",
             "config": {"workload": f"{args.workload}: two-layer GCN forward relu(A relu(A X W1) W2) on synthetic config 5, "
                                    f"N={n}, nnz={nnz}, max degree {info['max_degree']}, {n_blocks} .block4 tuples, 128 features, "
-                                   f"A row-sharded by nonzeros over {world} GPU(s), all-gather of X*W per layer",
+                                   f"A in row blocks (equal rows and nonzeros) over {world} GPU(s), all-gather of X*W per layer",
                        "n": n, "nnz": nnz, "n_blocks": n_blocks, "l2": "no flush: every operand is larger than L2"},
-            "per_layer_ms": {"gemm": gemm_ms, "all_gather": gather_ms, "spmm_relu": spmm_ms},
+            "per_layer_ms": per_layer,
             "roofline": {"bound": "hbm", "achieved": spmm_bytes / spmm_ms / 1e6, "peak": peak, "unit": "GB/s",
                          "frac": spmm_bytes / spmm_ms / 1e6 / peak, "traffic": None, "peak_source": peak_src,
                          "kernel": "spmm_units_kernel dim=128 (+ReLU), per rank",
@@ -546,15 +736,15 @@ def ours_gcn(args, rank, world, local_rank):
                          "gemm": {"kernel": "gemm_tf32_128_kernel", "achieved": gemm_bytes / gemm_ms / 1e6,
                                   "frac": gemm_bytes / gemm_ms / 1e6 / peak, "algorithmic_bytes_per_launch": gemm_bytes}},
             "clocks": clocks,
-            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 4 * 128 * n_loc, "d2h_bytes_per_step": 4 * 128 * n_loc,
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 4 * 128 * per, "d2h_bytes_per_step": 4 * 128 * per,
                     "steps": e2e_steps, "bit_identical_to_resident_run": same},
-            "gpu_launches": args.steps * 2 * (1 + shard.plan.info()["launches_last_run"]),
-            "plan": shard.plan.info(), "preprocess_ms": info.get("preprocess_ms")}
+            "gpu_launches": args.steps * 2 * (1 + shard.info()["launches_last_step"]),
+            "plan": shard.info(), "preprocess_ms": info.get("preprocess_ms"), "sampled_rows_check": sampled}
     if world == 1:
         # CPU baseline on a bounded sample: every k-th row of A (SpMM) and of H (X*W, numpy/BLAS)
         from oracle import oracle
         ix_h, v_h = ix_keep.cpu().numpy(), v_keep.cpu().numpy()
-        x_h = x_local.cpu().numpy()
+        x_h = shard.from_blocks([x_block]).cpu().numpy()
         gf, dt, desc, stride = cpu_spmm_rate(ip_h, ix_h, v_h, [x_h], args.cpu_seconds)
         rows = x_h[::stride]
         t0 = time.perf_counter()
@@ -566,6 +756,41 @@ def ours_gcn(args, rank, world, local_rank):
     else:
         dist.destroy_process_group()
     print(json.dumps(line), flush=True)
+
+
+def gcn_sampled_check(ip, ix, v, x_rows, w1, w2, out, dev, n_sample=48):
+    """Parity at sizes no CPU forward can check: for a sample of output rows the whole two-hop
+    computation is redone in fp64 on the device from the CSR arrays (single GPU: the block is the
+    whole matrix, so local row = matrix row = column id).  Rows of more than 2000 nonzeros are left
+    out of the sample to keep its two-hop fan-out bounded."""
+    import torch
+    n = int(ip.numel()) - 1
+    cand = torch.unique(torch.cat([torch.randint(0, n, (n_sample,), device=dev), torch.tensor([0, n // 2, n - 1], device=dev)]))
+    w1d, w2d = w1.double(), w2.double()
+
+    def neighbours(r):
+        a, b = int(ip[r]), int(ip[r + 1])
+        return ix[a:b].long(), v[a:b].double()
+
+    worst, used = 0.0, 0
+    scale = float(out.abs().max())
+    for r in cand.tolist():
+        c1, a1 = neighbours(r)
+        if c1.numel() > 2000:
+            continue
+        h1 = torch.zeros((c1.numel(), 128), dtype=torch.float64, device=dev)
+        for k, j in enumerate(c1.tolist()):
+            c2, a2 = neighbours(j)
+            if c2.numel() > 200_000:
+                break
+            h1[k] = torch.clamp((a2[:, None] * (x_rows(c2).double() @ w1d)).sum(0), min=0)
+        else:
+            ref = torch.clamp((a1[:, None] * (h1 @ w2d)).sum(0), min=0)
+            worst = max(worst, float((out[r].double() - ref).abs().max()))
+            used += 1
+    return {"rows_checked": used, "max_abs_err": worst, "output_scale": scale, "tolerance": 4e-3 * scale,
+            "ok": bool(used > 0 and worst <= 4e-3 * scale),
+            "what": "two-hop fp64 recomputation of sampled output rows on the device; tolerance 4e-3 of the output scale (TF32 dense transform)"}
 
 
 def ours_replicas(args):
@@ -618,6 +843,9 @@ def ours_replicas(args):
             row["max_abs_diff_vs_reference_kernel"] = float(err.max())
             row["accel_ms"] = oracle.ref_accel_spmm(b4_h, ip_h, ix_h, v_h, x_h, timing=True) * 1e3
             row["cusparse_ms"] = oracle.ref_cusparse_spmm(ip_h, ix_h, v_h, x_h, timing=True) * 1e3
+            if args.gnna and nnz <= 3_000_000:
+                # the reference's third kernel (spmm_gnna.cu, timed at main.cu:164-165); it ignores the values of A
+                row["gnna_ms"] = oracle.ref_gnna_time(ip_h, ix_h, v_h, x_h) * 1e3
         rows.append(row)
         tot_flops += 2.0 * nnz * dim
         tot_ms += ms
@@ -667,6 +895,11 @@ def main():
     ap.add_argument("--no-ref-gpu", action="store_true", help="skip timing the reference's GPU kernels")
     ap.add_argument("--dim", type=int, default=64, help="dense width of the replicas workload")
     ap.add_argument("--kernel-only", action="store_true", help="resident-data loop only (for profiling under ncu)")
+    ap.add_argument("--slices", type=int, default=1,
+                    help="N > 1: exchange the dense operand in this many row slices and multiply slice by slice")
+    ap.add_argument("--tiled", choices=("auto", "off"), default="auto",
+                    help="one GPU: run products whose X exceeds L2 column-tiled (auto) or never (off)")
+    ap.add_argument("--gnna", action="store_true", help="replicas workload: also time the reference's GNNAdvisor kernel")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -6,7 +6,9 @@ of libaccelgcn.so (include/accelgcn.h).
     spmm        -- SPMM_ACCEL plug-in mirror (do_test / run) and a functional call
     graphio     -- the reference's raw-binary graph and .block4 files
     synth       -- seeded synthetic graphs for tests and benchmarks
-    sharded     -- 1D row-sharded multi-GPU SpMM (torch.distributed plumbing)
+    sharded     -- 1D row-sharded multi-GPU SpMM (agcn_dist_*: layout, NCCL exchange and kernels in the library)
+    gcn         -- two-layer GCN forward on the row blocks (agcn_gcn2_forward_*)
+    gemm        -- dense feature transform on the tensor cores (agcn_gemm_tf32*)
 
 PyTorch appears here only as the owner of device memory and streams (and of the
 process group in `sharded`); all compute is in the shared library.

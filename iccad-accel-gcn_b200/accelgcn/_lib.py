@@ -39,7 +39,37 @@ PROTOTYPES = {
     "agcn_host_set_graph": (_int, [_vp, _vp, _i64, _vp, _vp, _i64, _i64, _i64]),
     "agcn_host_spmm": (_int, [_vp, _vp, _vp, _int]),
     "agcn_spmm_host": (_int, [_vp, _vp, _i64, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int]),
+    "agcn_host_spmm_batch": (_int, [_vp, _int, _vp, _vp, _vp]),
+    "agcn_spmm_host_batch": (_int, [_vp, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _int, _vp, _vp, _vp]),
+    "agcn_spmm_tiled_create": (_int, [ctypes.POINTER(_vp), _vp, _vp, _vp, _i64, _i64, _i64, _vp, _int, _vp]),
+    "agcn_spmm_tiled_run": (_int, [_vp, _vp, _i64, _vp, _i64, _int, _int, _vp]),
+    "agcn_spmm_tiled_run_range": (_int, [_vp, _int, _vp, _i64, _vp, _i64, _int, _int, _vp]),
+    "agcn_spmm_tiled_destroy": (_int, [_vp]),
+    "agcn_spmm_tiled_info": (_int, [_vp, ctypes.POINTER(_int), ctypes.POINTER(_i64), _vp, ctypes.POINTER(_int)]),
+    "agcn_spmm_tiled_suggest": (_int, [_i64, _i64, _i64, _int]),
+    "agcn_gemm_tf32_async": (_int, [_vp, _i64, _vp, _vp, _i64, _i64, _int, _int, _vp, _vp]),
+    "agcn_gemm_tf32_selftest_timeout": (_int, [_vp, _i64, _vp, _vp, _i64, _i64, _vp]),
+    "agcn_balanced_blocks": (_int, [_vp, _i64, _int, _vp, ctypes.POINTER(_i64)]),
+    "agcn_dist_unique_id": (_int, [_vp]),
+    "agcn_dist_create": (_int, [ctypes.POINTER(_vp), _int, _int, _vp]),
+    "agcn_dist_destroy": (_int, [_vp]),
+    "agcn_dist_set_graph": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _int, _vp]),
+    "agcn_dist_info": (_int, [_vp, ctypes.POINTER(_i64), ctypes.POINTER(_i64), ctypes.POINTER(_i64),
+                             ctypes.POINTER(_i64), ctypes.POINTER(_int), ctypes.POINTER(_int)]),
+    "agcn_dist_block_rows": (_int, [_vp, _int, _vp, _vp]),
+    "agcn_dist_gather_begin": (_int, [_vp, _int, _vp, _int, _vp]),
+    "agcn_dist_spmm_gathered": (_int, [_vp, _int, _vp, _int, _int, _vp]),
+    "agcn_dist_spmm_step": (_int, [_vp, _vp, _vp, _int, _int, _vp]),
+    "agcn_dist_spmm_on_gathered": (_int, [_vp, _vp, _vp, _int, _int, _vp]),
+    "agcn_dist_gathered": (_int, [_vp, _int, ctypes.POINTER(_vp), ctypes.POINTER(_i64)]),
+    "agcn_gcn2_forward_create": (_int, [ctypes.POINTER(_vp), _vp, _vp, _vp]),
+    "agcn_gcn2_forward_run": (_int, [_vp, _vp, _vp, _vp]),
+    "agcn_gcn2_forward_status": (_int, [_vp, _vp]),
+    "agcn_gcn2_forward_destroy": (_int, [_vp]),
+    "agcn_probe_gather_bandwidth": (_int, [_i64, _int, _i64, _int, ctypes.POINTER(ctypes.c_double)]),
 }
+DIST_ID_BYTES = 128
+MAX_WORLD = 64
 
 _lib = None
 

@@ -1,79 +1,62 @@
-"""Two-layer GCN forward  relu(A relu(A X W1) W2)  on the row-sharded operator.
+"""Two-layer GCN forward  relu(A relu(A X W1) W2)  on the row blocks of the sharded operator:
+the Python face of agcn_gcn2_forward_*.
 
-Per layer and per rank:  Z_local = H_local @ W  (agcn_gemm_tf32 on the rows this rank owns),
-all-gather Z over the ranks, H'_local = relu(A_shard @ Z)  (the SpMM with its fused ReLU).
-The reference stops at the SpMM; the layers are the workload its operator exists for.
+Per layer and per rank:  Z_block = H_block @ W  (tcgen05 TF32 GEMM on the rows this rank owns),
+all-gather of Z (NCCL, slice by slice), H'_block = relu(A_block @ Z) (the SpMM with its fused
+ReLU).  The reference stops at the SpMM; the layers are the workload its operator exists for.
+Everything is enqueued by the library on the caller's stream; this class owns only the handle.
 """
 from __future__ import annotations
 
-from . import gemm, sharded
+import ctypes
+
+from . import _lib, sharded
 
 
 class GcnForward:
-    """panel_cols: with more than one rank the all-gather of X*W is the longest part of a layer and
-    the SpMM cannot start on a row before all of its columns' rows have arrived -- but it can start
-    on a COLUMN panel as soon as that panel has.  With panel_cols = 32 or 64, X*W is exchanged in
-    panels of that many columns and the SpMM of panel p runs while panel p+1 is still in flight.
-    Off by default (panel_cols=None: exchange and multiply all columns at once): measured on two
-    B200s at N = 5e6 the panelled schedule was slower (10.5 against 8.4 ms per layer) -- four
-    32-column passes over an operand far larger than L2 cost more than one 128-column pass, and
-    they compete with the collective for HBM bandwidth while it runs."""
-
-    def __init__(self, shard: "sharded.ShardedSpmm", weights, panel_cols=None):
+    def __init__(self, shard: "sharded.ShardedSpmm", weights):
+        import torch
+        if len(weights) != 2:
+            raise ValueError("the native forward has two layers")
+        self._torch = torch
+        self._lib = _lib.load()
         self.shard = shard
-        self.weights = [w.contiguous() for w in weights]
-        self.panel_cols = panel_cols
-        self._bufs = {}
+        self.weights = [w.contiguous() for w in weights]       # borrowed by the handle: keep alive
+        for w in self.weights:
+            if tuple(w.shape) != (128, 128) or w.dtype != torch.float32 or not w.is_cuda:
+                raise TypeError("weights must be float32 CUDA tensors [128 x 128]")
+        h = ctypes.c_void_p()
+        with torch.cuda.device(shard.device):
+            _lib.check(self._lib.agcn_gcn2_forward_create(ctypes.byref(h), shard._h, self.weights[0].data_ptr(),
+                                                          self.weights[1].data_ptr()))
+        self._h = h
 
-    def _buf(self, name, rows, cols, like):
-        import torch
-        b = self._bufs.get(name)
-        if b is None or b.shape != (rows, cols):
-            b = torch.empty((rows, cols), dtype=torch.float32, device=like.device)
-            self._bufs[name] = b
-        return b
+    def forward(self, x_block, out=None, stream=None):
+        """x_block: this rank's block rows of X [rows_per_block, 128].  Returns this rank's block rows of
+        the output.  Asynchronous on the current stream; call `status()` after synchronising."""
+        torch = self._torch
+        if out is None:
+            out = torch.empty_like(x_block)
+        s = stream if stream is not None else torch.cuda.current_stream(self.shard.device)
+        rc = self._lib.agcn_gcn2_forward_run(self._h, x_block.data_ptr(), out.data_ptr(), s.cuda_stream)
+        if rc != 0:
+            _lib.check(rc)
+        return out
 
-    def forward(self, x_local, timings=None):
-        """x_local: this rank's rows of X [n_local, 128].  Returns this rank's rows of the output."""
-        import torch
-        sh = self.shard
-        h = x_local
-        for li, w in enumerate(self.weights):
-            ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)] if timings is not None else None
-            if ev: ev[0].record()
-            z = gemm.gemm_tf32(h, w, out=self._buf("z", sh.n_local, w.shape[1], h))
-            if ev: ev[1].record()
-            width = w.shape[1]
-            h_next = self._buf(f"h{li % 2}", sh.n_local, width, h)
-            if self.panel_cols is None:
-                if sh.world > 1:
-                    zg = sharded.all_gather_rows(z, sh.cuts, sh.rank, sh.world,
-                                                 out=self._buf("zg", sh.n_cols, width, h), group=sh.group)
-                else:
-                    zg = z
-                if ev: ev[2].record()
-                sh.plan.run(sh.indices, sh.vals, zg, h_next, dim=width, ldx=width, ldy=width, relu=True)
-            else:
-                pc = self.panel_cols
-                pending = []
-                for c0 in range(0, width, pc):
-                    c1 = min(width, c0 + pc)
-                    zp = self._buf(f"zp{c0}", sh.n_local, c1 - c0, h)
-                    zp.copy_(z[:, c0:c1])
-                    if sh.world > 1:
-                        pending.append(sharded.all_gather_rows(zp, sh.cuts, sh.rank, sh.world,
-                                                               out=self._buf(f"zg{c0}", sh.n_cols, c1 - c0, h),
-                                                               group=sh.group, async_op=True))
-                    else:
-                        pending.append((zp, None))
-                if ev: ev[2].record()          # all exchanges started; their time shows up in the SpMM span
-                for (zg, work), c0 in zip(pending, range(0, width, pc)):
-                    c1 = min(width, c0 + pc)
-                    if work is not None:
-                        work.wait()
-                    sh.plan.run(sh.indices, sh.vals, zg, h_next[:, c0:c1], dim=c1 - c0, ldx=c1 - c0, ldy=width, relu=True)
-            h = h_next
-            if ev:
-                ev[3].record()
-                timings.append(ev)
-        return h
+    def status(self, timings: bool = False):
+        """After a synchronise: raises if a dense transform's bounded wait ran out; with timings=True
+        returns per layer (gemm ms, wait for the first exchanged slice ms, spmm ms)."""
+        ms = (ctypes.c_float * 6)()
+        _lib.check(self._lib.agcn_gcn2_forward_status(self._h, ms if timings else None))
+        return [tuple(ms[3 * layer: 3 * layer + 3]) for layer in range(2)] if timings else None
+
+    def close(self):
+        if getattr(self, "_h", None) is not None and self._h.value:
+            self._lib.agcn_gcn2_forward_destroy(self._h)
+            self._h = ctypes.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

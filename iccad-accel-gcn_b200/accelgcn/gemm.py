@@ -20,3 +20,28 @@ def gemm_tf32(h, w, out=None, stream=None):
                                       z.data_ptr(), z.stride(0) if z.shape[0] > 1 else z.shape[1],
                                       h.shape[0], w.shape[0], w.shape[1], s.cuda_stream))
     return z
+
+
+def gemm_tf32_async(h, w, out, status, stream=None):
+    """The same product enqueued without waiting or allocating (agcn_gemm_tf32_async).  `status` is an
+    int32 CUDA tensor of one element the caller owns: 0 after the stream has been synchronised unless
+    a bounded wait inside the kernel ran out (1 producer, 2 MMA issuer, 3 epilogue)."""
+    import torch
+    lib = _lib.load()
+    s = stream if stream is not None else torch.cuda.current_stream(h.device)
+    with torch.cuda.device(h.device):
+        _lib.check(lib.agcn_gemm_tf32_async(h.data_ptr(), h.stride(0) if h.shape[0] > 1 else h.shape[1], w.data_ptr(),
+                                            out.data_ptr(), out.stride(0) if out.shape[0] > 1 else out.shape[1],
+                                            h.shape[0], w.shape[0], w.shape[1], status.data_ptr(), s.cuda_stream))
+    return out
+
+
+def selftest_timeout(h, w, out, stream=None) -> int:
+    """Runs the kernel's failure path on purpose (agcn_gemm_tf32_selftest_timeout) and returns the
+    status code of the call: ERR_CUDA when the starved wait ran out and the kernel left cleanly."""
+    import torch
+    lib = _lib.load()
+    s = stream if stream is not None else torch.cuda.current_stream(h.device)
+    with torch.cuda.device(h.device):
+        return lib.agcn_gemm_tf32_selftest_timeout(h.data_ptr(), h.stride(0), w.data_ptr(), out.data_ptr(), out.stride(0),
+                                                   h.shape[0], s.cuda_stream)

@@ -56,3 +56,34 @@ def write_graph(graph_dir: str, name: str, new_indptr, new_indices, orig_indptr=
     write_array(os.path.join(graph_dir, name + ".new_indices"), new_indices)
     write_array(os.path.join(graph_dir, name + ".graph.ptrdump"), new_indptr if orig_indptr is None else orig_indptr)
     write_array(os.path.join(graph_dir, name + ".graph.edgedump"), new_indices if orig_indices is None else orig_indices)
+
+
+def read_original_graph(graph_dir: str, name: str):
+    """The CSR in its original node order (main.cu:64-65)."""
+    return (read_array(os.path.join(graph_dir, name + ".graph.ptrdump")),
+            read_array(os.path.join(graph_dir, name + ".graph.edgedump")))
+
+
+def degree_sort_files(graph_dir: str, name: str, relabel_cols: bool = True):
+    """<name>.graph.ptrdump / .edgedump  ->  <name>.new_indptr / .new_indices: the degree-ordered
+    files the harness and the partitioner read (main.cu:62-63, block_level_partition.py:31-32).
+    The reference ships its graphs already ordered and has no code for this step; here it is one
+    call of the library's degree sort (rows ascending by degree, ties by original id, column ids
+    renamed by the same permutation unless relabel_cols is False).  The permutation is written
+    beside them as <name>.perm (perm[new_row] = original row) so that results can be put back in
+    the original order.  Returns (perm, new_indptr, new_indices)."""
+    from . import degree_sort
+    indptr, indices = read_original_graph(graph_dir, name)
+    perm, new_indptr, new_indices, _ = degree_sort.degree_sort(indptr, indices, None, relabel_cols=relabel_cols)
+    write_array(os.path.join(graph_dir, name + ".new_indptr"), new_indptr)
+    write_array(os.path.join(graph_dir, name + ".new_indices"), new_indices)
+    write_array(os.path.join(graph_dir, name + ".perm"), perm)
+    return perm, new_indptr, new_indices
+
+
+if __name__ == "__main__":
+    import sys
+    if len(sys.argv) != 3:
+        sys.exit("usage: python -m accelgcn.graphio <graph_dir> <name>    (degree-sorts <name>.graph.ptrdump/.edgedump)")
+    _perm, _ip, _ix = degree_sort_files(sys.argv[1], sys.argv[2])
+    print(f"{sys.argv[2]}: {len(_ip) - 1} rows, {len(_ix)} nonzeros -> .new_indptr / .new_indices / .perm")

@@ -1,176 +1,209 @@
-"""1D row-sharded multi-GPU SpMM: one process per GPU, torch.distributed for the
-exchange, libaccelgcn.so for every kernel.
+"""1D row-sharded multi-GPU SpMM: one process per GPU; the layout, the exchange (NCCL, inside
+libaccelgcn.so) and every kernel are the library's (agcn_dist_*).  This module only owns the
+tensors and hands the 128-byte communicator id from rank 0 to the others.
 
-The degree-ordered matrix A is cut at row boundaries into one contiguous row
-range per rank, balanced by nonzeros (not rows).  Each rank keeps its rows of
-A, its own `.block4` metadata (the partitioner run on the shard's row
-pointers -- the format is unchanged, row and nonzero offsets are shard-local)
-and the same rows of the dense operand.  One step is: all-gather the dense
-operand (the only exchange the path has), then the local SpMM.
+Layout.  Every rank holds two ranges of the degree-ordered rows, one from the light and one
+from the heavy end, chosen so that it has rows_per_block rows AND about nnz / world nonzeros
+(agcn_balanced_blocks).  Dense operands are "block rows": [rows_per_block x dim] per rank,
+padding rows zero; the all-gather of equal blocks is one balanced collective, and the gathered
+operand is a permutation of the degree order that the block's column ids were renamed to.
 
-Balancing by nonzeros makes the row counts very uneven (the first rank owns
-most of the light rows), so the exchange is an all-gather with a different
-block size per rank, straight into the [n x dim] operand in global row order:
-nothing is padded and column ids keep their global numbering.
-
-The reference has no multi-GPU code; this follows its single-GPU operator
-(spmm_accel.cu) shard by shard.
+The reference has no multi-GPU code; this follows its single-GPU operator (spmm_accel.cu)
+block by block.
 """
 from __future__ import annotations
 
+import ctypes
+
 import numpy as np
 
+from . import _lib
 
-def nnz_balanced_cuts(indptr, n_parts: int) -> np.ndarray:
-    """Row cut points c[0]=0 <= ... <= c[n_parts]=n_rows such that every range
-    [c[k], c[k+1]) holds about nnz / n_parts nonzeros.  Cuts fall on row
-    boundaries (a row is never split); indptr is a host array."""
+
+def balanced_blocks(indptr, world: int):
+    """Row ranges of every rank: (ranges int64 [world, 4] = light_begin, light_end, heavy_begin,
+    heavy_end; rows_per_block).  Host arrays only -- needs no GPU."""
+    lib = _lib.load()
+    indptr = np.ascontiguousarray(indptr, dtype=np.int32)
+    n = indptr.shape[0] - 1
+    ranges = np.zeros((world, 4), dtype=np.int64)
+    per = ctypes.c_int64(0)
+    _lib.check(lib.agcn_balanced_blocks(indptr.ctypes.data, n, world, ranges.ctypes.data, ctypes.byref(per)))
+    return ranges, per.value
+
+
+def block_rows(ranges, rows_per_block: int, rank: int) -> np.ndarray:
+    """Matrix row held at each local row of `rank` (-1 = padding): light rows, heavy rows, padding."""
+    la, lb, ha, hb = (int(v) for v in ranges[rank])
+    rows = np.concatenate([np.arange(la, lb), np.arange(ha, hb)]).astype(np.int64)
+    return np.concatenate([rows, np.full(rows_per_block - len(rows), -1, dtype=np.int64)])
+
+
+def gathered_position(rows_per_block: int, world: int, slices: int, rank: int) -> np.ndarray:
+    """Row of the gathered operand that holds each local row of `rank`'s block.  The operand is
+    exchanged in `slices` row slices: slice c of every rank comes first, then slice c + 1, ..."""
+    per = rows_per_block
+    assert per % slices == 0
+    bc = per // slices
+    j = np.arange(per, dtype=np.int64)
+    c, i = j // bc, j % bc
+    return c * (world * bc) + rank * bc + i
+
+
+def shard_csr(indptr, indices, vals, ranges, rows_per_block: int, world: int, slices: int, rank: int):
+    """Host restatement of what agcn_dist_set_graph builds on the device: the block's row pointers,
+    column ids renamed to gathered positions, values.  Used by the CPU tests with the oracle."""
     indptr = np.asarray(indptr, dtype=np.int64)
-    n_rows = len(indptr) - 1
-    nnz = int(indptr[-1] - indptr[0])
-    targets = indptr[0] + (np.arange(1, n_parts, dtype=np.int64) * nnz) // n_parts
-    inner = np.searchsorted(indptr, targets, side="left")
-    cuts = np.concatenate([[0], np.clip(inner, 0, n_rows), [n_rows]]).astype(np.int64)
-    return np.maximum.accumulate(cuts)
+    rows = block_rows(ranges, rows_per_block, rank)
+    valid = rows[rows >= 0]
+    deg = np.zeros(rows_per_block, dtype=np.int64)
+    deg[: len(valid)] = indptr[valid + 1] - indptr[valid]
+    ip = np.concatenate([[0], np.cumsum(deg)])
+    src = np.concatenate([np.arange(indptr[r], indptr[r + 1]) for r in valid] + [np.zeros(0, dtype=np.int64)]).astype(np.int64)
+    new_id = np.full(int(indptr.shape[0] - 1), -1, dtype=np.int64)
+    for g in range(world):
+        rg = block_rows(ranges, rows_per_block, g)
+        pos = gathered_position(rows_per_block, world, slices, g)
+        new_id[rg[rg >= 0]] = pos[rg >= 0]
+    return ip.astype(np.int32), new_id[np.asarray(indices)[src]].astype(np.int32), np.asarray(vals)[src]
 
 
-def shard_rows(indptr, indices, vals, cuts, rank: int):
-    """The rows [cuts[rank], cuts[rank+1]) of a CSR matrix, row pointers rebased to 0."""
-    r0, r1 = int(cuts[rank]), int(cuts[rank + 1])
-    p0, p1 = int(indptr[r0]), int(indptr[r1])
-    return indptr[r0:r1 + 1] - indptr[r0], indices[p0:p1], vals[p0:p1]
-
-
-def all_gather_rows(x_local, cuts, rank: int, world_size: int, out=None, group=None, async_op: bool = False):
-    """All-gather row blocks of different heights: rank r contributes rows [cuts[r], cuts[r+1]) of
-    the [n x dim] result.  On NCCL this is one all-gather call with per-rank sizes (grouped
-    broadcasts inside the library); on other backends (the gloo CPU tests) one broadcast per rank."""
-    import torch
+def exchange_id(rank: int, world: int, group=None) -> bytes | None:
+    """The communicator id: made by rank 0 inside the library, handed to the other ranks through
+    torch.distributed (any transport would do: it is 128 opaque bytes)."""
+    if world == 1:
+        return None
     import torch.distributed as dist
-    n, dim = int(cuts[-1]), x_local.shape[1]
-    if out is None:
-        out = torch.empty((n, dim), dtype=x_local.dtype, device=x_local.device)
-    if world_size == 1:
-        out.copy_(x_local)
-        return out
-    blocks = [out[int(cuts[r]):int(cuts[r + 1])] for r in range(world_size)]
-    if dist.get_backend(group) == "nccl":
-        work = dist.all_gather(blocks, x_local.contiguous(), group=group, async_op=async_op)
-        return (out, work) if async_op else out
-    else:
-        blocks[rank].copy_(x_local)
-        for r in range(world_size):
-            if blocks[r].numel():
-                dist.broadcast(blocks[r], src=dist.get_global_rank(group, r) if group is not None else r, group=group)
-    return (out, None) if async_op else out
-
-
-def even_rows(n: int, world_size: int) -> int:
-    """Rows per rank when the dense operand is block-distributed evenly (the last block is padded)."""
-    return -(-int(n) // int(world_size))
-
-
-def all_gather_even(x_block, world_size: int, out=None, group=None, async_op: bool = False):
-    """All-gather of equal blocks [rows_per_rank x dim] into [world_size * rows_per_rank x dim]:
-    one balanced collective (every rank sends the same amount), for a dense operand whose rows are
-    distributed evenly rather than along the nnz-balanced cuts of A."""
-    import torch
-    import torch.distributed as dist
-    per, dim = x_block.shape
-    if out is None:
-        out = torch.empty((world_size * per, dim), dtype=x_block.dtype, device=x_block.device)
-    if world_size == 1:
-        out.copy_(x_block)
-        return (out, None) if async_op else out
-    work = dist.all_gather_into_tensor(out, x_block.contiguous(), group=group, async_op=async_op)
-    return (out, work) if async_op else out
+    box = [None]
+    if rank == 0:
+        buf = ctypes.create_string_buffer(_lib.DIST_ID_BYTES)
+        _lib.check(_lib.load().agcn_dist_unique_id(buf))
+        box[0] = bytes(buf.raw)
+    src = dist.get_global_rank(group, 0) if group is not None else 0
+    dist.broadcast_object_list(box, src=src, group=group)
+    return box[0]
 
 
 class ShardedSpmm:
-    """This rank's shard of a degree-ordered A, ready to multiply.
+    """This rank's block of a degree-ordered square A, ready to multiply.
 
-    indptr / indices / vals are the FULL degree-ordered matrix as CUDA tensors
-    on this rank's device (every rank builds the same synthetic matrix from the
-    same seed, or loads the same files); the shard is cut out here."""
+    indptr / indices / vals are the WHOLE degree-ordered matrix as CUDA tensors on this rank's
+    device (every rank builds the same synthetic matrix from the same seed, or loads the same
+    files); the block is cut out inside the library.  `exchange_slices` > 1 exchanges the dense
+    operand in that many row slices and starts the product over a slice when it has arrived.
+    `communicator=False` builds the block without NCCL (the caller assembles the gathered operand
+    itself and calls `multiply_gathered`): used to run every rank's block in one process."""
 
-    def __init__(self, indptr, indices, vals, rank: int, world_size: int, group=None):
+    def __init__(self, indptr, indices, vals, rank: int, world_size: int, group=None, exchange_slices: int = 1,
+                 communicator: bool = True):
         import torch
-        from . import partition, spmm
-        self.rank, self.world, self.group = rank, world_size, group
-        self.n = indptr.numel() - 1
-        self.cuts = nnz_balanced_cuts(indptr.cpu().numpy(), world_size)
-        ip, ix, v = shard_rows(indptr, indices, vals, self.cuts, rank)
-        self.indptr = ip.contiguous()
-        self.vals = v.contiguous()
-        self.indices = ix.contiguous()
-        self.n_local = self.indptr.numel() - 1
-        self.n_cols = self.n
-        self.block4 = partition.block_level_partition_device(self.indptr)
-        self.plan = spmm.SpmmPlan(self.block4, self.indices, self.n_local, self.n_cols)
-        self._gather = {}
-        self.device = indptr.device
         self._torch = torch
+        self._lib = lib = _lib.load()
+        self.rank, self.world, self.group = int(rank), int(world_size), group
+        self.device = indptr.device
+        self.n = int(indptr.numel()) - 1
+        uid = exchange_id(self.rank, self.world, group) if communicator else None
+        h = ctypes.c_void_p()
+        with torch.cuda.device(self.device):
+            _lib.check(lib.agcn_dist_create(ctypes.byref(h), self.rank, self.world, uid))
+            self._h = h
+            s = torch.cuda.current_stream(self.device)
+            _lib.check(lib.agcn_dist_set_graph(h, indptr.data_ptr(), indices.data_ptr(), vals.data_ptr(), self.n,
+                                               int(indices.numel()), int(exchange_slices), s.cuda_stream))
+        info = self.info()
+        self.rows_per_block, self.slices = info["rows_per_block"], info["exchange_slices"]
+        self.local_rows, self.local_nnz, self.n_blocks = info["local_rows"], info["local_nnz"], info["n_blocks"]
+        self.n_gathered = self.rows_per_block * self.world
+        self._rows = {}
 
-    @property
-    def row_range(self):
-        return int(self.cuts[self.rank]), int(self.cuts[self.rank + 1])
+    def info(self) -> dict:
+        a, b, c, d = (ctypes.c_int64() for _ in range(4))
+        e, f = ctypes.c_int(), ctypes.c_int()
+        _lib.check(self._lib.agcn_dist_info(self._h, ctypes.byref(a), ctypes.byref(b), ctypes.byref(c), ctypes.byref(d),
+                                            ctypes.byref(e), ctypes.byref(f)))
+        return {"rows_per_block": a.value, "local_rows": b.value, "local_nnz": c.value, "n_blocks": d.value,
+                "exchange_slices": e.value, "launches_last_step": f.value}
 
-    def even_block(self, x_full_rows):
-        """This rank's block of an evenly distributed dense operand, given a callable or tensor that
-        yields rows [a, b) of it; the last rank's block is zero-padded to the common height."""
-        per = even_rows(self.n, self.world)
-        a, b = min(self.n, self.rank * per), min(self.n, (self.rank + 1) * per)
-        rows = x_full_rows(a, b) if callable(x_full_rows) else x_full_rows[a:b]
-        if rows.shape[0] == per:
-            return rows.contiguous()
-        blk = self._torch.zeros((per, rows.shape[1]), dtype=rows.dtype, device=rows.device)
-        blk[: rows.shape[0]] = rows
+    def rows_of(self, rank: int | None = None):
+        """int64 CUDA tensor [rows_per_block]: the matrix row at each local row of `rank` (-1 = padding)."""
+        torch = self._torch
+        rank = self.rank if rank is None else rank
+        if rank not in self._rows:
+            out = torch.empty(self.rows_per_block, dtype=torch.int32, device=self.device)
+            with torch.cuda.device(self.device):
+                _lib.check(self._lib.agcn_dist_block_rows(self._h, rank, out.data_ptr(),
+                                                          torch.cuda.current_stream(self.device).cuda_stream))
+            self._rows[rank] = out.to(torch.int64)
+        return self._rows[rank]
+
+    def to_block(self, x_rows):
+        """This rank's block rows [rows_per_block x dim] of a dense operand given in matrix order:
+        x_rows is a tensor [n x dim] or a callable rows -> tensor (for operands too large to build whole)."""
+        torch = self._torch
+        rows = self.rows_of()
+        valid = rows >= 0
+        picked = x_rows(rows[valid]) if callable(x_rows) else x_rows[rows[valid]]
+        blk = torch.zeros((self.rows_per_block, picked.shape[1]), dtype=torch.float32, device=self.device)
+        blk[valid] = picked
         return blk
 
-    def gather_even_async(self, x_block):
-        """Start the balanced all-gather of an evenly distributed operand (see all_gather_even);
-        returns (buffer, work).  Column ids index the buffer directly: block r starts at row
-        r * rows_per_rank = the global row id of its first row."""
-        dim = x_block.shape[1]
-        if self.world == 1:
-            return x_block, None
-        key = ("even", dim)
-        buf = self._gather.get(key)
-        if buf is None:
-            buf = self._torch.empty((self.world * x_block.shape[0], dim), dtype=x_block.dtype, device=self.device)
-            self._gather[key] = buf
-        return all_gather_even(x_block, self.world, out=buf, group=self.group, async_op=True)
+    def from_blocks(self, blocks):
+        """Matrix-order [n x dim] tensor from the block rows of every rank (tests, single process)."""
+        torch = self._torch
+        out = torch.empty((self.n, blocks[0].shape[1]), dtype=torch.float32, device=self.device)
+        for g, blk in enumerate(blocks):
+            rows = self.rows_of(g)
+            out[rows[rows >= 0]] = blk[rows >= 0]
+        return out
 
-    def gather_async(self, x_local):
-        """Start the all-gather of this rank's rows of the dense operand and return (buffer, work).
-        The collective runs on the process group's own stream; call work.wait() (it only makes the
-        current stream wait) before multiplying.  Gathers of independent operands can therefore be
-        in flight while earlier products are still being computed.  One buffer per width."""
-        dim = x_local.shape[1]
-        if self.world == 1:
-            return x_local, None
-        buf = self._gather.get(dim)
-        if buf is None:
-            buf = self._torch.empty((self.n_cols, dim), dtype=x_local.dtype, device=self.device)
-            self._gather[dim] = buf
-        return all_gather_rows(x_local, self.cuts, self.rank, self.world, out=buf, group=self.group, async_op=True)
+    def _stream(self, stream):
+        return (stream if stream is not None else self._torch.cuda.current_stream(self.device)).cuda_stream
 
-    def step(self, x_local, y_local, x_gathered=None):
-        """y_local[n_local x dim] = A_shard @ allgather(x_local).  Asynchronous on the current stream.
-        x_gathered, if given, is the already gathered [n x dim] operand (the collective is skipped)."""
-        dim = y_local.shape[1]
-        if x_gathered is not None:
-            x_full = x_gathered
-        elif self.world == 1:
-            x_full = x_local
-        else:
-            buf = self._gather.get(dim)
-            if buf is None:
-                buf = self._torch.empty((self.n_cols, dim), dtype=x_local.dtype, device=self.device)
-                self._gather[dim] = buf
-            x_full = all_gather_rows(x_local, self.cuts, self.rank, self.world, out=buf, group=self.group)
-        self.plan.run(self.indices, self.vals, x_full, y_local, dim=dim, ldx=dim, ldy=dim)
-        return y_local
+    def gather_begin(self, x_block, slot: int = 0, stream=None) -> None:
+        """Start the all-gather of this rank's block into `slot` (0..3), behind the work already on
+        the stream.  Exchanges of independent products can be started together."""
+        rc = self._lib.agcn_dist_gather_begin(self._h, slot, x_block.data_ptr(), int(x_block.shape[1]), self._stream(stream))
+        if rc != 0:
+            _lib.check(rc)
+
+    def multiply(self, y_block, slot: int = 0, relu: bool = False, stream=None) -> None:
+        """y_block = act(A_block @ gathered operand of `slot`); the stream waits for the exchange slice by slice."""
+        rc = self._lib.agcn_dist_spmm_gathered(self._h, slot, y_block.data_ptr(), int(y_block.shape[1]), 1 if relu else 0,
+                                               self._stream(stream))
+        if rc != 0:
+            _lib.check(rc)
+
+    def step(self, x_block, y_block, relu: bool = False, stream=None):
+        """One product: all-gather x_block, then y_block = act(A_block @ X).  Asynchronous."""
+        rc = self._lib.agcn_dist_spmm_step(self._h, x_block.data_ptr(), y_block.data_ptr(), int(y_block.shape[1]),
+                                           1 if relu else 0, self._stream(stream))
+        if rc != 0:
+            _lib.check(rc)
+        return y_block
+
+    def multiply_gathered(self, gathered, y_block, relu: bool = False, stream=None):
+        """The local product on a gathered operand [world * rows_per_block x dim] assembled by the caller."""
+        _lib.check(self._lib.agcn_dist_spmm_on_gathered(self._h, gathered.data_ptr(), y_block.data_ptr(), int(y_block.shape[1]),
+                                                        1 if relu else 0, self._stream(stream)))
+        return y_block
+
+    def assemble_gathered(self, blocks):
+        """What the all-gather produces from every rank's block (tests, single process)."""
+        torch = self._torch
+        dim = blocks[0].shape[1]
+        out = torch.empty((self.n_gathered, dim), dtype=torch.float32, device=self.device)
+        for g, blk in enumerate(blocks):
+            pos = torch.from_numpy(gathered_position(self.rows_per_block, self.world, self.slices, g)).to(self.device)
+            out[pos] = blk
+        return out
 
     def close(self):
-        self.plan.close()
+        if getattr(self, "_h", None) is not None and self._h.value:
+            self._lib.agcn_dist_destroy(self._h)
+            self._h = ctypes.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

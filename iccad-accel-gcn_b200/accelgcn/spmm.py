@@ -73,6 +73,61 @@ class SpmmPlan:
             pass
 
 
+class TiledSpmmPlan:
+    """Column-tiled product (agcn_spmm_tiled_*): A regrouped by column range so that every launch
+    gathers from one L2-resident slab of X; the first range stores Y, later ranges add to it.
+    `bounds` are the ascending column ids that start each range (from 0 to n_cols); without them
+    the library's suggestion for `dim` columns is used (equal ranges)."""
+
+    def __init__(self, indptr, indices, vals, n_rows: int, n_cols: int, bounds=None, dim: int = 128, stream=None):
+        import torch
+        lib = _lib.load()
+        self._lib, self.device = lib, indptr.device
+        nnz = int(indices.numel())
+        if bounds is None:
+            k = lib.agcn_spmm_tiled_suggest(int(n_rows), int(n_cols), nnz, int(dim))
+            bounds = [int(n_cols) * i // k for i in range(k + 1)]
+        self.bounds = np.ascontiguousarray(bounds, dtype=np.int32)
+        self.n_rows, self.n_cols = int(n_rows), int(n_cols)
+        s = stream if stream is not None else torch.cuda.current_stream(self.device)
+        h = ctypes.c_void_p()
+        with torch.cuda.device(self.device):
+            _lib.check(lib.agcn_spmm_tiled_create(ctypes.byref(h), indptr.data_ptr(), indices.data_ptr(), vals.data_ptr(),
+                                                  self.n_rows, self.n_cols, nnz, self.bounds.ctypes.data,
+                                                  len(self.bounds) - 1, s.cuda_stream))
+        self._h = h
+
+    def run(self, x, y, relu: bool = False, stream=None, only_range: int | None = None) -> None:
+        import torch
+        s = stream if stream is not None else torch.cuda.current_stream(self.device)
+        dim, ldx, ldy = int(x.shape[1]), int(x.stride(0)), int(y.stride(0))
+        with torch.cuda.device(self.device):
+            if only_range is None:
+                rc = self._lib.agcn_spmm_tiled_run(self._h, x.data_ptr(), ldx, y.data_ptr(), ldy, dim, 1 if relu else 0, s.cuda_stream)
+            else:
+                rc = self._lib.agcn_spmm_tiled_run_range(self._h, int(only_range), x.data_ptr(), ldx, y.data_ptr(), ldy, dim,
+                                                         1 if relu else 0, s.cuda_stream)
+        if rc != 0:
+            _lib.check(rc)
+
+    def info(self) -> dict:
+        k, nb, ln = ctypes.c_int(), ctypes.c_int64(), ctypes.c_int()
+        rn = (ctypes.c_int64 * 32)()
+        _lib.check(self._lib.agcn_spmm_tiled_info(self._h, ctypes.byref(k), ctypes.byref(nb), rn, ctypes.byref(ln)))
+        return {"n_ranges": k.value, "n_blocks": nb.value, "range_nnz": list(rn)[: k.value], "launches_last_run": ln.value}
+
+    def close(self) -> None:
+        if getattr(self, "_h", None) is not None and self._h.value:
+            self._lib.agcn_spmm_tiled_destroy(self._h)
+            self._h = ctypes.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 def spmm(block4, indices, vals, x, n_rows: int | None = None, out=None):
     """Y = A @ X on the device.  block4 [n_blocks,4] int32, indices int32, vals fp32, x [n_cols, dim] fp32."""
     import torch
@@ -165,6 +220,33 @@ class HostSpmm:
         y = out if out is not None else np.empty((self._n_rows, dim), dtype=np.float32)
         _lib.check(self._lib.agcn_host_spmm(self._h, _addr(x), _addr(y), dim))
         return y
+
+    def run_batch(self, xs, outs=None):
+        """Several products enqueued together (agcn_host_spmm_batch): uploads, kernels and downloads overlap."""
+        n = len(xs)
+        for x in xs:
+            if x.shape[0] != self._n_cols:
+                raise ValueError("X has the wrong number of rows")
+        ys = outs if outs is not None else [np.empty((self._n_rows, x.shape[1]), dtype=np.float32) for x in xs]
+        px = (ctypes.c_void_p * n)(*[_addr(x) for x in xs])
+        py = (ctypes.c_void_p * n)(*[_addr(y) for y in ys])
+        dims = (ctypes.c_int * n)(*[int(x.shape[1]) for x in xs])
+        _lib.check(self._lib.agcn_host_spmm_batch(self._h, n, px, py, dims))
+        return ys
+
+    def step_batch(self, block4, indices, vals, xs, n_rows: int, outs=None):
+        """The graph and several products in one call (agcn_spmm_host_batch): A goes up in ranges and
+        every range is multiplied as soon as it has arrived."""
+        n = len(xs)
+        n_cols = xs[0].shape[0]
+        self._n_rows, self._n_cols = int(n_rows), int(n_cols)
+        ys = outs if outs is not None else [np.empty((n_rows, x.shape[1]), dtype=np.float32) for x in xs]
+        px = (ctypes.c_void_p * n)(*[_addr(x) for x in xs])
+        py = (ctypes.c_void_p * n)(*[_addr(y) for y in ys])
+        dims = (ctypes.c_int * n)(*[int(x.shape[1]) for x in xs])
+        _lib.check(self._lib.agcn_spmm_host_batch(self._h, _addr(block4), _numel(block4) // 4, _addr(indices), _addr(vals),
+                                                  n_rows, n_cols, _numel(indices), n, px, py, dims))
+        return ys
 
     def __call__(self, block4, indices, vals, x, n_rows: int, out=None):
         n_cols, dim = x.shape

@@ -50,6 +50,17 @@ def splitmix64(seed: int, stream: int, start: int, count: int, device) -> torch.
     return z ^ _lsr(z, 31)
 
 
+def uniform_f32_at(seed, stream, index: torch.Tensor, lo: float, hi: float) -> torch.Tensor:
+    """Elements `index` (int64 tensor, any shape) of the stream uniform_f32(seed, stream, 0, ...) draws from:
+    the generator is counter-based, so any subset can be produced without the rest."""
+    base = _s64(seed + ((stream * 0x100000001B3) & _MASK64))
+    z = (index + 1) * _GOLDEN + base
+    z = (z ^ _lsr(z, 30)) * _M1
+    z = (z ^ _lsr(z, 27)) * _M2
+    r = _lsr(z ^ _lsr(z, 31), 40).to(torch.float32)
+    return r * ((hi - lo) / float(1 << 24)) + lo
+
+
 def uniform_int(seed, stream, start, count, bound: int, device) -> torch.Tensor:
     """Integers in [0, bound) (bound < 2^62); the modulo bias is below 2^-1."""
     r = _lsr(splitmix64(seed, stream, start, count, device), 1)    # 63 random bits, non-negative

@@ -71,3 +71,29 @@ def test_bad_input_is_an_error_not_a_fault():
         degree_sort.degree_sort(np.array([0, 2, 1], dtype=np.int32), np.array([0, 1], dtype=np.int32))
     with pytest.raises(AccelGcnError):       # column 9 cannot be relabelled in a 2-row matrix
         degree_sort.degree_sort(np.array([0, 1, 2], dtype=np.int32), np.array([0, 9], dtype=np.int32), relabel_cols=True)
+
+
+def test_values_given_but_not_wanted_and_wrong_nnz():
+    # the C ABI allows d_vals != NULL with d_new_vals == NULL (the values are simply not permuted),
+    # and rejects an nnz that is not the matrix's own count instead of reading past the arrays
+    import ctypes
+    import torch
+    from accelgcn import _lib, synth
+    dev = require_cuda()
+    lib = _lib.load()
+    g = synth.make_config(1, dev, 0.25)
+    n, nnz = g.n, g.nnz
+    perm = torch.empty(n, dtype=torch.int32, device=dev)
+    nip = torch.empty(n + 1, dtype=torch.int32, device=dev)
+    nix = torch.full((nnz,), -1, dtype=torch.int32, device=dev)
+    rc = lib.agcn_degree_sort_device(g.indptr.data_ptr(), g.indices.data_ptr(), g.vals.data_ptr(), n, nnz, 1,
+                                     perm.data_ptr(), nip.data_ptr(), nix.data_ptr(), None, None)
+    assert rc == _lib.OK, lib.agcn_last_error()
+    torch.cuda.synchronize()
+    want = oracle.degree_sort(g.indptr.cpu().numpy(), g.indices.cpu().numpy(), None, True)
+    assert np.array_equal(perm.cpu().numpy(), want[0]) and np.array_equal(nix.cpu().numpy(), want[2])
+    for wrong in (nnz + 4096, nnz - 1):
+        rc = lib.agcn_degree_sort_device(g.indptr.data_ptr(), g.indices.data_ptr(), None, n, wrong, 0,
+                                         perm.data_ptr(), nip.data_ptr(), nix.data_ptr(), None, None)
+        assert rc == _lib.ERR_INVALID and b"nnz" in lib.agcn_last_error()
+    torch.cuda.synchronize()

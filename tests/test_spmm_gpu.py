@@ -234,29 +234,39 @@ def test_parity_with_the_reference_kernel_heavy_rows(cfg4_small):
     assert spmm_close(y, cs, row_abs_scale(cfg4_small.indptr, cfg4_small.val, x)).all()
 
 
-@pytest.mark.parametrize("world", [2, 5])
-def test_row_sharded_product_on_one_gpu_equals_unsharded(cfg4_small, world):
-    # every rank's shard built and multiplied in this one process (the all-gather is replaced by
-    # handing over the full operand): shard-local .block4 and row offsets, global column ids
+@pytest.mark.parametrize("world,slices", [(2, 1), (5, 1), (4, 3), (8, 2)])
+def test_row_sharded_product_on_one_gpu_equals_unsharded(cfg4_small, world, slices):
+    # every rank's block built and multiplied in this one process (contexts without a communicator:
+    # the all-gather is replaced by assembling the gathered operand by hand): two row ranges per
+    # rank, column ids renamed to gathered positions, block-local .block4
     import torch
     from accelgcn import sharded
     c = cfg4_small
     dev = c.dev
     ip, ix, v = (torch.from_numpy(a).to(dev) for a in (c.indptr, c.idx, c.val))
     x = c.x(64)
-    parts = []
-    for r in range(world):
-        sh = sharded.ShardedSpmm(ip, ix, v, r, world)
-        xg = torch.from_numpy(x).to(dev)              # what the all-gather assembles: X in global row order
-        y = torch.full((sh.n_local, 64), float("nan"), dtype=torch.float32, device=dev)
-        sh.step(None, y, x_gathered=xg)
-        torch.cuda.synchronize()
-        parts.append(y.cpu().numpy())
-        sh.close()
-    y = np.concatenate(parts)
+    xt = torch.from_numpy(x).to(dev)
+    shards = [sharded.ShardedSpmm(ip, ix, v, r, world, exchange_slices=slices, communicator=False) for r in range(world)]
+    gathered = shards[0].assemble_gathered([sh.to_block(xt) for sh in shards])
+    blocks = []
+    for sh in shards:
+        y = torch.full((sh.rows_per_block, 64), float("nan"), dtype=torch.float32, device=dev)
+        sh.multiply_gathered(gathered, y)
+        blocks.append(y)
+    torch.cuda.synchronize()
+    y = shards[0].from_blocks(blocks).cpu().numpy()
     c.check(x, y)
-    nnz_per_rank = np.diff(c.indptr[sharded.nnz_balanced_cuts(c.indptr, world)].astype(np.int64))
-    assert nnz_per_rank.max() - nnz_per_rank.min() <= 2 * np.diff(c.indptr).max()
+    for sh, blk in zip(shards, blocks):                        # padding rows multiply to zero
+        assert torch.all(blk[sh.rows_of() < 0] == 0)
+    # the device layout is the host layout (agcn_balanced_blocks), and it balances rows and nonzeros
+    ranges, per = sharded.balanced_blocks(c.indptr, world)
+    per = -(-per // slices) * slices
+    for r, sh in enumerate(shards):
+        assert sh.rows_per_block == per and np.array_equal(sh.rows_of().cpu().numpy(), sharded.block_rows(ranges, per, r))
+    nnz = np.array([sh.local_nnz for sh in shards])
+    assert nnz.sum() == len(c.idx) and nnz.max() - nnz.min() <= 2 * np.diff(c.indptr).max()
+    for sh in shards:
+        sh.close()
 
 
 def test_cpp_harness_same_cli_and_output_as_the_reference(cfg1, tmp_path):
@@ -344,3 +354,279 @@ def test_full_size_config2_checksum_and_sampled_rows():
         ref = (v[a:b].to(torch.float64)[:, None] * x[ix[a:b].to(torch.int64)].to(torch.float64)).sum(0)
         err = (y1[r].to(torch.float64) - ref).abs()
         assert bool((err <= 1e-5 + 1e-4 * ref.abs()).all()), int(r)
+
+
+# ----------------------------------------------------------------------------------------
+# the configurations at the sizes the benchmark numbers are quoted on
+# ----------------------------------------------------------------------------------------
+def _full_config_on_device(cfg):
+    import torch
+    from accelgcn import synth, degree_sort, partition
+    dev = require_cuda()
+    g = synth.make_config(cfg, dev, 1.0)
+    _, ip, ix, v = degree_sort.degree_sort_device(g.indptr, g.indices, g.vals, relabel_cols=True)
+    b4 = partition.block_level_partition_device(ip)
+    seed = g.info["seed"]
+    n = g.n
+    del g
+    torch.cuda.empty_cache()
+    return dev, n, seed, ip, ix, v, b4
+
+
+def _checksum_and_rows(n, ip, ix, v, x, y, n_sample=200):
+    """1^T (A X) = (1^T A) X in fp64, and a row sample (with the lightest and the heaviest rows)
+    against the fp64 product, at the parity tolerance rel 1e-4 / abs 1e-5 scaled by the row's
+    absolute sum."""
+    import torch
+    dev = x.device
+    assert not torch.isnan(y).any()
+    col_weight = torch.zeros(n, dtype=torch.float64, device=dev).index_add_(0, ix.to(torch.int64), v.to(torch.float64))
+    want = col_weight @ x.to(torch.float64)
+    got = y.to(torch.float64).sum(0)
+    assert torch.allclose(got, want, rtol=1e-6, atol=1e-6 * float(col_weight.abs().sum())), float((got - want).abs().max())
+    ip_h = ip.cpu().numpy()
+    rows = np.unique(np.concatenate([np.random.default_rng(0).integers(0, n, n_sample), [0, 1, n - 3, n - 2, n - 1]]))
+    xmax = float(x.abs().max())
+    for r in rows:
+        a, b = int(ip_h[r]), int(ip_h[r + 1])
+        ref = (v[a:b].to(torch.float64)[:, None] * x[ix[a:b].to(torch.int64)].to(torch.float64)).sum(0)
+        scale = max(1.0, float(v[a:b].abs().sum()) * xmax)
+        err = (y[r].to(torch.float64) - ref).abs()
+        assert bool((err <= 1e-5 * scale + 1e-4 * ref.abs()).all()), (int(r), float(err.max()))
+
+
+@pytest.fixture(scope="module")
+def cfg2_full():
+    return _full_config_on_device(2)
+
+
+@pytest.mark.parametrize("dim", [32, 128])
+def test_full_size_config2_other_widths(cfg2_full, dim):
+    # dim 128 is the launch the benchmark's roofline is quoted on, and the only one where the
+    # two 64-column passes are chosen automatically (X = 128 MB against a 126 MB L2)
+    import torch
+    from accelgcn import synth, spmm
+    dev, n, seed, ip, ix, v, b4 = cfg2_full
+    x = synth.features(n, dim, seed, dev)
+    plan = spmm.SpmmPlan(b4, ix, n, n)
+    y = torch.full((n, dim), float("nan"), device=dev)
+    plan.run(ix, v, x, y)
+    torch.cuda.synchronize()
+    launches = plan.info()["launches_last_run"]
+    plan.close()
+    if dim == 128:
+        assert launches >= 2            # two column passes (plus the carry kernels if any row crosses units)
+    _checksum_and_rows(n, ip, ix, v, x, y)
+
+
+def test_full_size_config2_column_tiled(cfg2_full):
+    # the column-tiled product at dim 128 (3 ranges): same checks, and within the parity tolerance of
+    # the un-tiled product element by element (only the order of the fp32 additions differs)
+    import torch
+    from accelgcn import synth, spmm, _lib
+    dev, n, seed, ip, ix, v, b4 = cfg2_full
+    x = synth.features(n, 128, seed, dev)
+    k = _lib.load().agcn_spmm_tiled_suggest(n, n, int(ix.numel()), 128)
+    assert 2 <= k <= 8
+    tiled = spmm.TiledSpmmPlan(ip, ix, v, n, n, dim=128)
+    assert tiled.info()["n_ranges"] == k and sum(tiled.info()["range_nnz"]) == int(ix.numel())
+    y1 = torch.full((n, 128), float("nan"), device=dev)
+    y2 = torch.full((n, 128), 3.0, device=dev)
+    tiled.run(x, y1)
+    tiled.run(x, y2)
+    torch.cuda.synchronize()
+    tiled.close()
+    assert torch.equal(y1, y2)                               # bit-identical from run to run
+    _checksum_and_rows(n, ip, ix, v, x, y1)
+    plan = spmm.SpmmPlan(b4, ix, n, n)
+    y0 = torch.empty((n, 128), device=dev)
+    plan.run(ix, v, x, y0)
+    torch.cuda.synchronize()
+    plan.close()
+    assert bool(((y1 - y0).abs() <= 1e-5 + 1e-4 * y0.abs()).all())
+
+
+@pytest.mark.parametrize("panel", [32, 64])
+def test_forced_column_passes_on_small_graphs(cfg1, cfg4_small, panel, monkeypatch):
+    # AGCN_SPMM_PANEL (read at plan creation) forces the pass loop -- and the reuse of the carry
+    # scratch between passes -- on inputs small enough for the full oracle
+    monkeypatch.setenv("AGCN_SPMM_PANEL", str(panel))
+    for case in (cfg1, cfg4_small):
+        for dim in (128, 100, 61):
+            x = case.x(dim)
+            case.check(x, case.run(x))
+
+
+def test_full_size_config3():
+    # N = 2 400 000, ~6e7 nonzeros, dim 64: the whole product against the CPU oracle (fp64 accumulation)
+    import torch
+    from accelgcn import synth, spmm
+    dev, n, seed, ip, ix, v, b4 = _full_config_on_device(3)
+    x = synth.features(n, 64, seed, dev)
+    y = torch.full((n, 64), float("nan"), device=dev)
+    spmm.spmm(b4, ix, v, x, n, out=y)
+    oracle.use_all_host_threads()
+    ip_h, ix_h, v_h, x_h = ip.cpu().numpy(), ix.cpu().numpy(), v.cpu().numpy(), x.cpu().numpy()
+    ref = oracle.spmm_csr(ip_h, ix_h, v_h, x_h)
+    ok = spmm_close(y.cpu().numpy(), ref, row_abs_scale(ip_h, v_h, x_h))
+    assert ok.all(), f"{(~ok).sum()} elements out of tolerance, first at {np.argwhere(~ok)[0]}"
+
+
+@pytest.fixture(scope="module")
+def cfg4_full():
+    dev, n, seed, ip, ix, v, b4 = _full_config_on_device(4)
+    host = {k: t.cpu().numpy() for k, t in (("ip", ip), ("ix", ix), ("v", v), ("b4", b4))}
+    return dev, n, seed, ip, ix, v, b4, host
+
+
+@pytest.mark.parametrize("dim", list(range(16, 129, 4)))
+def test_full_size_config4_sweep(cfg4_full, dim):
+    # N = 500 000, max degree ~9e4, every width of the configuration: against the CPU oracle and
+    # (where it was built) against the reference's own kernel on the same arrays
+    import torch
+    from accelgcn import synth, spmm
+    dev, n, seed, ip, ix, v, b4, h = cfg4_full
+    x = synth.features(n, dim, seed, dev)
+    y = torch.full((n, dim), float("nan"), device=dev)
+    spmm.spmm(b4, ix, v, x, n, out=y)
+    y_h, x_h = y.cpu().numpy(), x.cpu().numpy()
+    oracle.use_all_host_threads()
+    scale = row_abs_scale(h["ip"], h["v"], x_h)
+    ok = spmm_close(y_h, oracle.spmm_csr(h["ip"], h["ix"], h["v"], x_h), scale)
+    assert ok.all(), f"{(~ok).sum()} elements out of tolerance, first at {np.argwhere(~ok)[0]}"
+    if oracle.ref_available() and dim % 16 == 0:
+        ref = oracle.ref_accel_spmm(h["b4"], h["ip"], h["ix"], h["v"], x_h)
+        assert spmm_close(y_h, ref, scale).all()
+
+
+@pytest.mark.parametrize("dim", [17, 61, 99, 127])
+def test_unaligned_widths_padded_copy_equals_scalar_path(cfg4_small, dim, monkeypatch):
+    # dims that are not multiples of 4: the default copies X into aligned rows and runs the 16-byte
+    # path; AGCN_SPMM_PAD=0 keeps the 4-byte gathers.  Both against the oracle, and equal to each other
+    # within the tolerance (the order of additions inside a row differs between the two).
+    x = cfg4_small.x(dim)
+    y_pad = cfg4_small.run(x)
+    cfg4_small.check(x, y_pad)
+    monkeypatch.setenv("AGCN_SPMM_PAD", "0")
+    y_scalar = cfg4_small.run(x)
+    cfg4_small.check(x, y_scalar)
+    assert spmm_close(y_pad, y_scalar, row_abs_scale(cfg4_small.indptr, cfg4_small.val, x)).all()
+
+
+@pytest.mark.parametrize("case_name", ["cfg1", "cfg4_small"])
+def test_column_tiled_small(case_name, request):
+    # tiled plan with several range layouts (one of them empty), ReLU, an unaligned width and the
+    # range-by-range entry, against the oracle
+    import torch
+    from accelgcn import spmm
+    c = request.getfixturevalue(case_name)
+    dev = c.dev
+    ip = torch.from_numpy(c.indptr).to(dev)
+    n = c.n
+    for bounds in ([0, n], [0, n // 2, n], [0, n // 3, n // 3, n - 5, n]):
+        tiled = spmm.TiledSpmmPlan(ip, c.t["idx"], c.t["val"], n, n, bounds=bounds)
+        for dim, relu in ((64, False), (128, True), (33, True)):
+            x = c.x(dim)
+            xt = torch.from_numpy(x).to(dev)
+            y = torch.full((n, dim), float("nan"), device=dev)
+            tiled.run(xt, y, relu=relu)
+            y2 = torch.full((n, dim), float("nan"), device=dev)
+            for k in range(len(bounds) - 1):
+                tiled.run(xt, y2, relu=relu, only_range=k)
+            torch.cuda.synchronize()
+            assert torch.equal(y, y2)
+            ref = oracle.spmm_csr(c.indptr, c.idx, c.val, x)
+            if relu:
+                ref = np.maximum(ref, 0)
+            assert spmm_close(y.cpu().numpy(), ref, row_abs_scale(c.indptr, c.val, x)).all(), (bounds, dim)
+        tiled.close()
+
+
+def test_host_batch_and_streamed_graph(cfg1, cfg4_small):
+    # the pipelined host-buffer calls: several products on a resident graph, and graph + products in
+    # one call (A uploaded and multiplied range by range); bit-identical to the one-product call
+    import torch
+    from accelgcn import spmm
+    for c in (cfg1, cfg4_small):
+        h = spmm.HostSpmm()
+        dims = [32, 64, 128, 60, 33]
+        xs = [np.ascontiguousarray(c.x(d)) for d in dims]
+        ys = h.step_batch(c.block4, c.idx, c.val, xs[:4], c.n)              # streamed (all widths multiples of 4)
+        for x, y in zip(xs[:4], ys):
+            c.check(x, y)
+        ys_all = h.step_batch(c.block4, c.idx, c.val, xs, c.n)              # 33 columns: upload first, then multiply
+        for x, y in zip(xs, ys_all):
+            c.check(x, y)
+        h.set_graph(c.block4, c.idx, c.val, c.n, c.n)
+        ys_res = h.run_batch(xs)
+        for a, b in zip(ys_all, ys_res):
+            assert np.array_equal(a, b)
+        for x, y in zip(xs, ys_res):
+            assert np.array_equal(h.run(x), y)
+        for a, b in zip(ys, ys_res[:4]):
+            assert np.array_equal(a, b)
+        # pinned buffers take the same path
+        px = [torch.from_numpy(x).pin_memory() for x in xs[:3]]
+        py = [torch.empty((c.n, d), dtype=torch.float32).pin_memory() for d in dims[:3]]
+        h.run_batch(px, outs=py)
+        for y, ref in zip(py, ys_res[:3]):
+            assert np.array_equal(y.numpy(), ref)
+        # a column id out of range is rejected (by the check that runs ahead of each range), nothing faults
+        bad = c.idx.copy()
+        bad[len(bad) // 2] = c.n + 7
+        with pytest.raises(spmm._lib.AccelGcnError, match="column index"):
+            h.step_batch(c.block4, bad, c.val, xs[:3], c.n)
+        ys_again = h.step_batch(c.block4, c.idx, c.val, xs[:3], c.n)        # and the context is still good
+        for a, b in zip(ys_again, ys_res[:3]):
+            assert np.array_equal(a, b)
+        h.close()
+
+
+def test_cpp_harness_full_sweep_mode(cfg1, tmp_path):
+    # spmm_test with no arguments: every graph of ../graphs at every dim 16..128 step 1
+    # (main.cu:195-219), here on two small graphs; with checking forced on, every product validates
+    import subprocess, importlib.util
+    from conftest import PKG
+    from accelgcn import graphio, degree_sort, partition, synth
+    spec = importlib.util.spec_from_file_location("agcn_build", os.path.join(PKG, "build.py"))
+    mod = importlib.util.module_from_spec(spec); spec.loader.exec_module(mod)
+    exe = mod.build_harness()
+    os.makedirs(tmp_path / "block_level_meta"); os.makedirs(tmp_path / "build")
+    graphio.write_graph(str(tmp_path / "graphs"), "synth1", cfg1.indptr, cfg1.idx)
+    graphio.write_block4(str(tmp_path / "block_level_meta" / "synth1.block4"), cfg1.block4)
+    g = synth.make_config(4, "cpu", 0.004)
+    _, ip, ix, _ = degree_sort.degree_sort(g.indptr.numpy(), g.indices.numpy(), None)
+    graphio.write_graph(str(tmp_path / "graphs"), "synth4", ip, ix)
+    graphio.write_block4(str(tmp_path / "block_level_meta" / "synth4.block4"), partition.block_level_partition(ip))
+    env = dict(os.environ, AGCN_TEST_CHECK_ALL="1")
+    out = subprocess.run([exe], cwd=tmp_path / "build", capture_output=True, text=True, timeout=1200, env=env)
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
+    assert "validation fail!" not in out.stdout
+    accel = [l.split() for l in out.stdout.splitlines() if " accel " in l]
+    assert len(accel) == 2 * 113 and {l[1] for l in accel} == {"synth1", "synth4"}
+    assert sorted({int(l[2]) for l in accel}) == list(range(16, 129))
+    assert out.stdout.count("validation pass!") == 2 * 113
+
+
+def test_degree_sort_files_front_end(tmp_path):
+    # original-order files -> .new_indptr / .new_indices / .perm, as one library call
+    from accelgcn import graphio, synth
+    g = synth.make_config(1, "cpu", 0.25)
+    ip, ix = g.indptr.numpy(), g.indices.numpy()
+    d = str(tmp_path / "graphs")
+    graphio.write_graph(d, "g", np.zeros(1, np.int32), np.zeros(0, np.int32), orig_indptr=ip, orig_indices=ix)
+    perm, nip, nix = graphio.degree_sort_files(d, "g")
+    want = oracle.degree_sort(ip, ix, None, True)
+    assert np.array_equal(perm, want[0]) and np.array_equal(nip, want[1]) and np.array_equal(nix, want[2])
+    rip, rix = graphio.read_sorted_graph(d, "g")
+    assert np.array_equal(rip, nip) and np.array_equal(rix, nix)
+    assert np.array_equal(graphio.read_array(os.path.join(d, "g.perm")), perm)
+
+
+def test_gather_probe_runs():
+    import ctypes
+    from accelgcn import _lib
+    require_cuda()
+    gbs = ctypes.c_double(0.0)
+    _lib.check(_lib.load().agcn_probe_gather_bandwidth(1 << 16, 64, 1 << 22, 3, ctypes.byref(gbs)))
+    assert gbs.value > 100.0            # GB/s: any working GPU is far above this
