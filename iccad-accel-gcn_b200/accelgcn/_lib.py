@@ -66,7 +66,7 @@ PROTOTYPES = {
     "agcn_gcn2_forward_run": (_int, [_vp, _vp, _vp, _vp]),
     "agcn_gcn2_forward_status": (_int, [_vp, _vp]),
     "agcn_gcn2_forward_destroy": (_int, [_vp]),
-    "agcn_probe_gather_bandwidth": (_int, [_i64, _int, _i64, _int, ctypes.POINTER(ctypes.c_double)]),
+    "agcn_probe_gather_bandwidth": (_int, [_i64, _int, _i64, _int, _int, ctypes.POINTER(ctypes.c_double)]),
 }
 DIST_ID_BYTES = 128
 MAX_WORLD = 64

@@ -3,7 +3,7 @@
 // L2 -> SM path for 4 * dim * N bytes from HBM, so on dense graphs its ceiling is this gather rate,
 // not the HBM bandwidth.  The probe issues the same access shape as the SpMM's float4 mode -- a
 // slot of dim/4 lanes reads one row with 16-byte loads, four independent rows in flight per lane,
-// the same residency (256 threads, 5 thread blocks per SM), the same L2 policy -- with row numbers
+// 256 threads per block at a residency the caller chooses, the same L2 policy -- with row numbers
 // from a counter-based hash instead of a column array and a plain add instead of the FMA, so what
 // it measures is the memory path alone.
 #include "host_common.h"
@@ -21,7 +21,7 @@ __device__ __forceinline__ uint32_t probe_hash(uint32_t x)
 }
 
 template <int S>
-__global__ void __launch_bounds__(256, 5)
+__global__ void __launch_bounds__(256)
 probe_gather_kernel(const float *__restrict__ table, uint32_t table_rows, int row_floats, int rows_per_warp, float *__restrict__ sink)
 {
     constexpr int NS = 32 / S;
@@ -48,7 +48,8 @@ probe_gather_kernel(const float *__restrict__ table, uint32_t table_rows, int ro
 
 // table_rows rows of row_floats floats (32, 64 or 128: 128 / 256 / 512-byte rows); total_rows rows
 // are gathered per launch; the rate over `iters` launches (after one warm-up) is returned in GB/s.
-extern "C" int agcn_probe_gather_bandwidth(int64_t table_rows, int row_floats, int64_t total_rows, int iters, double *gb_per_s)
+extern "C" int agcn_probe_gather_bandwidth(int64_t table_rows, int row_floats, int64_t total_rows, int iters,
+                                           int resident_blocks, double *gb_per_s)
 {
     using namespace agcn;
     clear_error();
@@ -56,6 +57,7 @@ extern "C" int agcn_probe_gather_bandwidth(int64_t table_rows, int row_floats, i
     AGCN_REQUIRE(row_floats == 32 || row_floats == 64 || row_floats == 128, "agcn_probe_gather_bandwidth: row_floats must be 32, 64 or 128");
     AGCN_REQUIRE(table_rows > 0 && table_rows < ((int64_t)1 << 31) && total_rows > 0 && iters >= 1,
                  "agcn_probe_gather_bandwidth: bad sizes");
+    AGCN_REQUIRE(resident_blocks >= 0 && resident_blocks <= 8, "agcn_probe_gather_bandwidth: resident_blocks must be 0..8");
     const int rows_per_warp = 4096;
     const int64_t warps = ceil_div(total_rows, rows_per_warp);
     AGCN_REQUIRE(warps / 8 + 1 < ((int64_t)1 << 31), "agcn_probe_gather_bandwidth: too many rows per launch");
@@ -67,10 +69,18 @@ extern "C" int agcn_probe_gather_bandwidth(int64_t table_rows, int row_floats, i
     cudaEvent_t e0 = nullptr, e1 = nullptr;
     AGCN_CUDA(cudaEventCreate(&e0));
     AGCN_CUDA(cudaEventCreate(&e1));
+    // resident_blocks > 0: unused dynamic shared memory sized so that only that many thread blocks fit
+    // on an SM (the SpMM keeps 5); 0 = whatever the registers allow
+    const size_t smem = resident_blocks == 0 ? 0 : (size_t)(220 * 1024 / resident_blocks) & ~(size_t)1023;
+    if (smem > 48 * 1024) {
+        AGCN_CUDA(cudaFuncSetAttribute(probe_gather_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        AGCN_CUDA(cudaFuncSetAttribute(probe_gather_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        AGCN_CUDA(cudaFuncSetAttribute(probe_gather_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    }
     auto launch = [&]() {
-        if (row_floats == 32) probe_gather_kernel<8><<<grid, 256>>>(table, (uint32_t)table_rows, row_floats, rows_per_warp, sink);
-        else if (row_floats == 64) probe_gather_kernel<16><<<grid, 256>>>(table, (uint32_t)table_rows, row_floats, rows_per_warp, sink);
-        else probe_gather_kernel<32><<<grid, 256>>>(table, (uint32_t)table_rows, row_floats, rows_per_warp, sink);
+        if (row_floats == 32) probe_gather_kernel<8><<<grid, 256, smem>>>(table, (uint32_t)table_rows, row_floats, rows_per_warp, sink);
+        else if (row_floats == 64) probe_gather_kernel<16><<<grid, 256, smem>>>(table, (uint32_t)table_rows, row_floats, rows_per_warp, sink);
+        else probe_gather_kernel<32><<<grid, 256, smem>>>(table, (uint32_t)table_rows, row_floats, rows_per_warp, sink);
     };
     launch();                                             // warm-up: brings the table into L2
     cudaError_t e = cudaGetLastError();

@@ -374,10 +374,11 @@ int agcn_gcn2_forward_destroy(agcn_gcn2 *fwd);
  * Measurement aid (not on the product path): the rate, in GB/s, at which this
  * GPU gathers whole rows of an L2-resident table with the access shape of the
  * SpMM (16-byte lanes, four rows in flight per lane, same residency and L2
- * policy) -- the ceiling of a gather SpMM on graphs dense enough that X is
+ * policy, a chosen number of resident thread blocks per SM) -- the ceiling of a gather SpMM on graphs dense enough that X is
  * re-read from L2 rather than from HBM.  row_floats is 32, 64 or 128.
  * ---------------------------------------------------------------------- */
 int agcn_probe_gather_bandwidth(int64_t table_rows, int row_floats, int64_t total_rows, int iters,
+                                int resident_blocks /* per SM; 0 = no limit, the SpMM keeps 5 */,
                                 double *gb_per_s);
 
 #ifdef __cplusplus

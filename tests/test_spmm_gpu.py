@@ -628,5 +628,5 @@ def test_gather_probe_runs():
     from accelgcn import _lib
     require_cuda()
     gbs = ctypes.c_double(0.0)
-    _lib.check(_lib.load().agcn_probe_gather_bandwidth(1 << 16, 64, 1 << 22, 3, ctypes.byref(gbs)))
+    _lib.check(_lib.load().agcn_probe_gather_bandwidth(1 << 16, 64, 1 << 22, 3, 5, ctypes.byref(gbs)))
     assert gbs.value > 100.0            # GB/s: any working GPU is far above this
