@@ -58,7 +58,7 @@ extern "C" int agcn_probe_gather_bandwidth(int64_t table_rows, int row_floats, i
     AGCN_REQUIRE(table_rows > 0 && table_rows < ((int64_t)1 << 31) && total_rows > 0 && iters >= 1,
                  "agcn_probe_gather_bandwidth: bad sizes");
     AGCN_REQUIRE(resident_blocks >= 0 && resident_blocks <= 8, "agcn_probe_gather_bandwidth: resident_blocks must be 0..8");
-    const int rows_per_warp = 4096;
+    const int rows_per_warp = 512;       // short warps, many of them: the grid must fill every SM several times over
     const int64_t warps = ceil_div(total_rows, rows_per_warp);
     AGCN_REQUIRE(warps / 8 + 1 < ((int64_t)1 << 31), "agcn_probe_gather_bandwidth: too many rows per launch");
     const unsigned grid = (unsigned)ceil_div(warps, 8);
