@@ -373,7 +373,6 @@ def ours(args, rank, world, local_rank):
 
     g, ip, ix, v, dims = build_workload(args.workload, dev)
     n, nnz = g.n, int(ix.numel())
-    assert len(dims) <= 4, "one exchange slot per product of a step"
     # one block of A per rank (two row ranges: equal rows and equal nonzeros); the dense operands and
     # results are block rows.  On one GPU the block is the whole matrix and nothing is exchanged.
     shard = sharded.ShardedSpmm(ip, ix, v, rank, world, exchange_slices=args.slices if world > 1 else 1)
@@ -399,20 +398,23 @@ def ours(args, rank, world, local_rank):
     def step(record=None):
         # the products of a step are independent: all their exchanges are started first (on the
         # library's communication stream), and each SpMM waits only for its own operand, slice by slice
-        if world > 1:
-            for di, d in enumerate(dims):
-                shard.gather_begin(xs[d], slot=di)
-        for di, d in enumerate(dims):
-            if record is not None:
-                record[di][0].record()
-            if d in tiled:
-                tiled[d].run(xs[d], ys[d])
-            elif world > 1:
-                shard.multiply(ys[d], slot=di)
-            else:
-                shard.step(xs[d], ys[d])
-            if record is not None:
-                record[di][1].record()
+        # (four exchange slots: widths are taken four at a time)
+        for g0 in range(0, len(dims), 4):
+            group = list(enumerate(dims))[g0:g0 + 4]
+            if world > 1:
+                for di, d in group:
+                    shard.gather_begin(xs[d], slot=di % 4)
+            for di, d in group:
+                if record is not None:
+                    record[di][0].record()
+                if d in tiled:
+                    tiled[d].run(xs[d], ys[d])
+                elif world > 1:
+                    shard.multiply(ys[d], slot=di % 4)
+                else:
+                    shard.step(xs[d], ys[d])
+                if record is not None:
+                    record[di][1].record()
 
     def count_launches():
         total = 0
@@ -420,7 +422,7 @@ def ours(args, rank, world, local_rank):
             if d in tiled:
                 tiled[d].run(xs[d], ys[d]); total += tiled[d].info()["launches_last_run"]
             elif world > 1:
-                shard.gather_begin(xs[d], slot=di); shard.multiply(ys[d], slot=di); total += shard.info()["launches_last_step"]
+                shard.gather_begin(xs[d], slot=di % 4); shard.multiply(ys[d], slot=di % 4); total += shard.info()["launches_last_step"]
             else:
                 shard.step(xs[d], ys[d]); total += shard.info()["launches_last_step"]
         return total
@@ -483,8 +485,8 @@ def ours(args, rank, world, local_rank):
             return float(tt.item())
 
         def only_products():
-            for di, d in enumerate(dims):
-                shard.multiply(ys[d], slot=di)
+            for di, d in list(enumerate(dims))[-4:]:        # the operands still in the four slots
+                shard.multiply(ys[d], slot=di % 4)
 
         compute_ms = timed_loop(only_products)
         nnz_local = torch.tensor([shard.local_nnz], dtype=torch.float64, device=dev)
@@ -637,11 +639,13 @@ def e2e_sharded(args, shard, xs, ys, dims, dev, world, barrier, flops_step):
     def step():
         for d in dims:
             xd[d].copy_(hx[d], non_blocking=True)
-        for di, d in enumerate(dims):
-            shard.gather_begin(xd[d], slot=di)
-        for di, d in enumerate(dims):
-            shard.multiply(ys[d], slot=di)
-            hy[d].copy_(ys[d], non_blocking=True)
+        for g0 in range(0, len(dims), 4):
+            group = list(enumerate(dims))[g0:g0 + 4]
+            for di, d in group:
+                shard.gather_begin(xd[d], slot=di % 4)
+            for di, d in group:
+                shard.multiply(ys[d], slot=di % 4)
+                hy[d].copy_(ys[d], non_blocking=True)
         torch.cuda.synchronize(dev)
 
     reps = max(1, min(args.steps, 5))
@@ -852,8 +856,8 @@ def gcn_sampled_check(ip, ix, v, x_rows, w1, w2, out_block, block_rows, dev, n_s
         if c1.numel() > 2000:
             continue
         h1 = torch.zeros((c1.numel(), 128), dtype=torch.float64, device=dev)
-        for k, j in enumerate(c1.tolist()):
-            c2, a2 = neighbours(j)
+        for k, col in enumerate(c1.tolist()):
+            c2, a2 = neighbours(col)
             if c2.numel() > 200_000:
                 break
             h1[k] = torch.clamp((a2[:, None] * (x_rows(c2).double() @ w1d)).sum(0), min=0)
@@ -973,7 +977,11 @@ def main():
     ap.add_argument("--tiled", choices=("auto", "off"), default="auto",
                     help="one GPU: run products whose X exceeds L2 column-tiled (auto) or never (off)")
     ap.add_argument("--gnna", action="store_true", help="replicas workload: also time the reference's GNNAdvisor kernel")
+    ap.add_argument("--dims", type=str, default="", help="comma-separated dense widths instead of the workload's own")
     args = ap.parse_args()
+    if args.dims:
+        cfg_id, scale, _ = WORKLOADS[args.workload]
+        WORKLOADS[args.workload] = (cfg_id, scale, tuple(int(t) for t in args.dims.split(",")))
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
