@@ -375,7 +375,15 @@ def ours(args, rank, world, local_rank):
     n, nnz = g.n, int(ix.numel())
     # one block of A per rank (two row ranges: equal rows and equal nonzeros); the dense operands and
     # results are block rows.  On one GPU the block is the whole matrix and nothing is exchanged.
-    shard = sharded.ShardedSpmm(ip, ix, v, rank, world, exchange_slices=args.slices if world > 1 else 1)
+    # (--slices S: widths of at least --slices-min-dim columns exchange their operand in S row slices and
+    # multiply slice by slice, on a second context of the same layout; narrower widths keep one slice)
+    sliced = world > 1 and args.slices > 1
+    shard = sharded.ShardedSpmm(ip, ix, v, rank, world)
+    shard_of = {d: shard for d in dims}
+    if sliced and any(d >= args.slices_min_dim for d in dims):
+        shard_sliced = sharded.ShardedSpmm(ip, ix, v, rank, world, exchange_slices=args.slices)
+        assert shard_sliced.rows_per_block == shard.rows_per_block, "--slices must divide the block height"
+        shard_of.update({d: shard_sliced for d in dims if d >= args.slices_min_dim})
     per = shard.rows_per_block
     n_blocks_local = int(shard.n_blocks)
     nb = torch.tensor([n_blocks_local], dtype=torch.int64, device=dev)
@@ -403,14 +411,14 @@ def ours(args, rank, world, local_rank):
             group = list(enumerate(dims))[g0:g0 + 4]
             if world > 1:
                 for di, d in group:
-                    shard.gather_begin(xs[d], slot=di % 4)
+                    shard_of[d].gather_begin(xs[d], slot=di % 4)
             for di, d in group:
                 if record is not None:
                     record[di][0].record()
                 if d in tiled:
                     tiled[d].run(xs[d], ys[d])
                 elif world > 1:
-                    shard.multiply(ys[d], slot=di % 4)
+                    shard_of[d].multiply(ys[d], slot=di % 4)
                 else:
                     shard.step(xs[d], ys[d])
                 if record is not None:
@@ -422,7 +430,8 @@ def ours(args, rank, world, local_rank):
             if d in tiled:
                 tiled[d].run(xs[d], ys[d]); total += tiled[d].info()["launches_last_run"]
             elif world > 1:
-                shard.gather_begin(xs[d], slot=di % 4); shard.multiply(ys[d], slot=di % 4); total += shard.info()["launches_last_step"]
+                shard_of[d].gather_begin(xs[d], slot=di % 4); shard_of[d].multiply(ys[d], slot=di % 4)
+                total += shard_of[d].info()["launches_last_step"]
             else:
                 shard.step(xs[d], ys[d]); total += shard.info()["launches_last_step"]
         return total
@@ -486,14 +495,22 @@ def ours(args, rank, world, local_rank):
 
         def only_products():
             for di, d in list(enumerate(dims))[-4:]:        # the operands still in the four slots
-                shard.multiply(ys[d], slot=di % 4)
+                shard_of[d].multiply(ys[d], slot=di % 4)
+
+        def only_exchanges():
+            for di, d in list(enumerate(dims))[-4:]:
+                shard_of[d].gather_begin(xs[d], slot=di % 4)
+            for di, d in list(enumerate(dims))[-4:]:
+                shard_of[d].wait_gathered(slot=di % 4)
 
         compute_ms = timed_loop(only_products)
+        exchange_ms = timed_loop(only_exchanges)
         nnz_local = torch.tensor([shard.local_nnz], dtype=torch.float64, device=dev)
         nnz_max = nnz_local.clone(); dist.all_reduce(nnz_max, op=dist.ReduceOp.MAX)
         multi = {"step_ms": total_ms / args.steps, "products_without_exchange_ms": compute_ms,
-                 "exchange_and_wait_ms": total_ms / args.steps - compute_ms,
-                 "exchange_slices": shard.slices,
+                 "exchanges_without_products_ms": exchange_ms, "exchange": os.environ.get("AGCN_DIST_EXCHANGE", "nccl all-gather"),
+                 "step_minus_products_ms": total_ms / args.steps - compute_ms,
+                 "exchange_slices": {str(d): shard_of[d].slices for d in dims},
                  "rows_per_block": per, "max_local_nnz_over_mean": float(nnz_max.item()) * world / nnz,
                  "exchanged_bytes_in_per_rank_per_step": 4 * sum(dims) * per * (world - 1),
                  "limiting_phase": "products" if compute_ms > 0.5 * total_ms / args.steps else "exchange"}
@@ -560,7 +577,7 @@ def ours(args, rank, world, local_rank):
                                   "note": "graph uploaded once at set-up (SPMM_BASE constructor), X and Y cross PCIe every step"}}
     host.close()
     if world > 1:
-        e2e = e2e_sharded(args, shard, xs, ys, dims, dev, world, barrier, flops_step)
+        e2e = e2e_sharded(args, shard_of, xs, ys, dims, dev, world, barrier, flops_step)
 
     if rank != 0:
         if world > 1:
@@ -627,7 +644,7 @@ def ours(args, rank, world, local_rank):
     print(json.dumps(line), flush=True)
 
 
-def e2e_sharded(args, shard, xs, ys, dims, dev, world, barrier, flops_step):
+def e2e_sharded(args, shard_of, xs, ys, dims, dev, world, barrier, flops_step):
     """End to end on several GPUs: every rank's block rows of X go up from pinned host memory, the
     step (exchange + products) runs, its block rows of Y come down -- all inside the timed region."""
     import torch
@@ -642,9 +659,9 @@ def e2e_sharded(args, shard, xs, ys, dims, dev, world, barrier, flops_step):
         for g0 in range(0, len(dims), 4):
             group = list(enumerate(dims))[g0:g0 + 4]
             for di, d in group:
-                shard.gather_begin(xd[d], slot=di % 4)
+                shard_of[d].gather_begin(xd[d], slot=di % 4)
             for di, d in group:
-                shard.multiply(ys[d], slot=di % 4)
+                shard_of[d].multiply(ys[d], slot=di % 4)
                 hy[d].copy_(ys[d], non_blocking=True)
         torch.cuda.synchronize(dev)
 
@@ -658,7 +675,7 @@ def e2e_sharded(args, shard, xs, ys, dims, dev, world, barrier, flops_step):
     dt = torch.tensor([time.perf_counter() - t0], dtype=torch.float64, device=dev)
     dist.all_reduce(dt, op=dist.ReduceOp.MAX)
     same = all(bool(torch.equal(hy[d], ys[d].cpu())) for d in dims)
-    per = shard.rows_per_block
+    per = shard_of[dims[0]].rows_per_block
     return {"value": flops_step * reps / float(dt.item()) / 1e9, "unit": UNIT,
             "h2d_bytes_per_step": sum(4 * d * per for d in dims), "d2h_bytes_per_step": sum(4 * d * per for d in dims),
             "steps": reps, "ms_per_step": float(dt.item()) / reps * 1e3, "bit_identical_to_resident_run": same,
@@ -974,6 +991,7 @@ def main():
     ap.add_argument("--kernel-only", action="store_true", help="resident-data loop only (for profiling under ncu)")
     ap.add_argument("--slices", type=int, default=1,
                     help="N > 1: exchange the dense operand in this many row slices and multiply slice by slice")
+    ap.add_argument("--slices-min-dim", type=int, default=128, help="narrowest width that --slices applies to (SpMM workloads)")
     ap.add_argument("--tiled", choices=("auto", "off"), default="auto",
                     help="one GPU: run products whose X exceeds L2 column-tiled (auto) or never (off)")
     ap.add_argument("--gnna", action="store_true", help="replicas workload: also time the reference's GNNAdvisor kernel")

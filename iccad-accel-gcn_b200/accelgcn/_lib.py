@@ -60,6 +60,7 @@ PROTOTYPES = {
     "agcn_dist_gather_begin": (_int, [_vp, _int, _vp, _int, _vp]),
     "agcn_dist_spmm_gathered": (_int, [_vp, _int, _vp, _int, _int, _vp]),
     "agcn_dist_spmm_step": (_int, [_vp, _vp, _vp, _int, _int, _vp]),
+    "agcn_dist_wait_gathered": (_int, [_vp, _int, _vp]),
     "agcn_dist_spmm_on_gathered": (_int, [_vp, _vp, _vp, _int, _int, _vp]),
     "agcn_dist_gathered": (_int, [_vp, _int, ctypes.POINTER(_vp), ctypes.POINTER(_i64)]),
     "agcn_gcn2_forward_create": (_int, [ctypes.POINTER(_vp), _vp, _vp, _vp]),

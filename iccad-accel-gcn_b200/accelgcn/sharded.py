@@ -173,6 +173,10 @@ class ShardedSpmm:
         if rc != 0:
             _lib.check(rc)
 
+    def wait_gathered(self, slot: int = 0, stream=None) -> None:
+        """Make the stream wait for the whole exchange of `slot` without multiplying."""
+        _lib.check(self._lib.agcn_dist_wait_gathered(self._h, slot, self._stream(stream)))
+
     def step(self, x_block, y_block, relu: bool = False, stream=None):
         """One product: all-gather x_block, then y_block = act(A_block @ X).  Asynchronous."""
         rc = self._lib.agcn_dist_spmm_step(self._h, x_block.data_ptr(), y_block.data_ptr(), int(y_block.shape[1]),

@@ -35,6 +35,7 @@ struct NcclApi {
     ncclResult_t (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int) = nullptr;
     ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
     ncclResult_t (*AllGather)(const void *, void *, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*AllReduce)(const void *, void *, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
     const char *(*GetErrorString)(ncclResult_t) = nullptr;
 };
 
@@ -54,8 +55,9 @@ static int nccl_api(const NcclApi **out)
         api.CommInitRank = reinterpret_cast<decltype(api.CommInitRank)>(dlsym(h, "ncclCommInitRank"));
         api.CommDestroy = reinterpret_cast<decltype(api.CommDestroy)>(dlsym(h, "ncclCommDestroy"));
         api.AllGather = reinterpret_cast<decltype(api.AllGather)>(dlsym(h, "ncclAllGather"));
+        api.AllReduce = reinterpret_cast<decltype(api.AllReduce)>(dlsym(h, "ncclAllReduce"));
         api.GetErrorString = reinterpret_cast<decltype(api.GetErrorString)>(dlsym(h, "ncclGetErrorString"));
-        if (!api.GetUniqueId || !api.CommInitRank || !api.CommDestroy || !api.AllGather || !api.GetErrorString) {
+        if (!api.GetUniqueId || !api.CommInitRank || !api.CommDestroy || !api.AllGather || !api.AllReduce || !api.GetErrorString) {
             set_error("agcn_dist: libnccl.so.2 lacks a needed symbol");
             dlclose(h);
             return AGCN_ERR_CUDA;
@@ -102,6 +104,15 @@ struct agcn_dist {
     cudaEvent_t ev_input = nullptr;                                        // the caller's block is ready on its stream
     bool slot_used[agcn::DIST_SLOTS] = {};
     int launches_last_step = 0;
+    // push exchange (AGCN_DIST_EXCHANGE=push): every rank copies its block straight into every peer's
+    // gathered buffer with the copy engines; two buffers per slot, used alternately
+    int push = 0;
+    float *pbuf[agcn::DIST_SLOTS][2] = {};                              // this rank's buffers
+    float *pbuf_peer[agcn::DIST_SLOTS][2][agcn::DIST_MAX_WORLD] = {};   // the same buffers of every rank, mapped here
+    size_t pbuf_cap[agcn::DIST_SLOTS] = {};
+    int pbuf_next[agcn::DIST_SLOTS] = {};
+    float *d_token = nullptr;                                           // one float: operand of the barrier all-reduce
+    unsigned char *d_handles = nullptr;                                 // [world][64]: exchange of IPC handles
 };
 
 struct agcn_gcn2 {
@@ -133,6 +144,14 @@ static void dist_free(agcn_dist *d)
         if (d->ev_consumed[s]) cudaEventDestroy(d->ev_consumed[s]);
     }
     if (d->ev_input) cudaEventDestroy(d->ev_input);
+    for (int s = 0; s < DIST_SLOTS; s++)
+        for (int b = 0; b < 2; b++) {
+            for (int r = 0; r < d->world; r++)
+                if (r != d->rank && d->pbuf_peer[s][b][r] != nullptr) cudaIpcCloseMemHandle(d->pbuf_peer[s][b][r]);
+            cudaFree(d->pbuf[s][b]);
+        }
+    cudaFree(d->d_token);
+    cudaFree(d->d_handles);
     if (d->comm != nullptr && d->nccl != nullptr) d->nccl->CommDestroy(d->comm);
     if (d->s_comm) cudaStreamDestroy(d->s_comm);
     delete d;
@@ -160,6 +179,11 @@ static int dist_create(agcn_dist **out, int rank, int world, const void *id)
         static_assert(sizeof(uid) == AGCN_DIST_ID_BYTES, "AGCN_DIST_ID_BYTES must be sizeof(ncclUniqueId)");
         memcpy(&uid, id, sizeof(uid));
         AGCN_NCCL(d->nccl, d->nccl->CommInitRank(&d->comm, world, uid, rank));
+        const char *mode = getenv("AGCN_DIST_EXCHANGE");
+        d->push = mode != nullptr && strcmp(mode, "push") == 0 ? 1 : 0;
+        AGCN_CUDA(cudaMalloc(&d->d_token, sizeof(float)));
+        AGCN_CUDA(cudaMemset(d->d_token, 0, sizeof(float)));
+        AGCN_CUDA(cudaMalloc(&d->d_handles, (size_t)world * sizeof(cudaIpcMemHandle_t)));
     }
     guard.d = nullptr;
     *out = d;
@@ -250,6 +274,90 @@ static int dist_set_graph(agcn_dist *d, const int *d_indptr, const int *d_indice
     return agcn_spmm_tiled_info(d->tiled, nullptr, &d->n_blocks, nullptr, nullptr);
 }
 
+// All ranks have reached this point of their communication streams (a one-float all-reduce).
+static int dist_barrier(agcn_dist *d)
+{
+    AGCN_NCCL(d->nccl, d->nccl->AllReduce(d->d_token, d->d_token, 1, ncclFloat, ncclSum, d->comm, d->s_comm));
+    return AGCN_OK;
+}
+
+// (Re)allocates the two push buffers of a slot on every rank and maps every peer's buffers here.
+// Collective: every rank calls it for the same slot and size at the same point of its program.
+static int dist_push_buffers(agcn_dist *d, int slot, size_t need)
+{
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    // nobody may still be copying into, or reading from, the old buffers
+    int rc = dist_barrier(d);
+    if (rc != AGCN_OK) return rc;
+    AGCN_CUDA(cudaStreamSynchronize(d->s_comm));
+    AGCN_CUDA(cudaDeviceSynchronize());
+    for (int b = 0; b < 2; b++)
+        for (int r = 0; r < d->world; r++) {
+            if (r != d->rank && d->pbuf_peer[slot][b][r] != nullptr) AGCN_CUDA(cudaIpcCloseMemHandle(d->pbuf_peer[slot][b][r]));
+            d->pbuf_peer[slot][b][r] = nullptr;
+        }
+    rc = dist_barrier(d);                      // every mapping of the old buffers is closed before they are freed
+    if (rc != AGCN_OK) return rc;
+    AGCN_CUDA(cudaStreamSynchronize(d->s_comm));
+    for (int b = 0; b < 2; b++) {
+        if (d->pbuf[slot][b] != nullptr) AGCN_CUDA(cudaFree(d->pbuf[slot][b]));
+        d->pbuf[slot][b] = nullptr;
+    }
+    d->pbuf_cap[slot] = 0;
+    for (int b = 0; b < 2; b++) {
+        AGCN_CUDA(cudaMalloc(&d->pbuf[slot][b], need));
+        cudaIpcMemHandle_t mine;
+        AGCN_CUDA(cudaIpcGetMemHandle(&mine, d->pbuf[slot][b]));
+        AGCN_CUDA(cudaMemcpyAsync(d->d_handles + (size_t)d->rank * sizeof(mine), &mine, sizeof(mine), cudaMemcpyHostToDevice, d->s_comm));
+        AGCN_NCCL(d->nccl, d->nccl->AllGather(d->d_handles + (size_t)d->rank * sizeof(mine), d->d_handles, sizeof(mine), ncclChar,
+                                             d->comm, d->s_comm));
+        std::vector<cudaIpcMemHandle_t> all((size_t)d->world);
+        AGCN_CUDA(cudaMemcpyAsync(all.data(), d->d_handles, (size_t)d->world * sizeof(mine), cudaMemcpyDeviceToHost, d->s_comm));
+        AGCN_CUDA(cudaStreamSynchronize(d->s_comm));
+        for (int r = 0; r < d->world; r++) {
+            if (r == d->rank) { d->pbuf_peer[slot][b][r] = d->pbuf[slot][b]; continue; }
+            void *p = nullptr;
+            AGCN_CUDA(cudaIpcOpenMemHandle(&p, all[r], cudaIpcMemLazyEnablePeerAccess));
+            d->pbuf_peer[slot][b][r] = static_cast<float *>(p);
+        }
+    }
+    d->pbuf_cap[slot] = need;
+    d->pbuf_next[slot] = 0;
+    return AGCN_OK;
+}
+
+// The exchange by copy engines: this rank's block goes straight into every rank's gathered buffer
+// (peer copies over NVLink, no SM is used), then a one-float all-reduce tells every rank that all
+// copies into its buffer have completed.  The slot's two buffers alternate: a buffer is written
+// again two exchanges later, and the barrier of the exchange in between already proves that every
+// rank has finished the product that read it (a slot's product must be enqueued before the slot's
+// next exchange is begun).
+static int dist_push(agcn_dist *d, int slot, const float *d_x_block, int dim)
+{
+    const size_t need = (size_t)d->n_gathered * dim * sizeof(float);
+    if (need > d->pbuf_cap[slot]) {
+        int rc = dist_push_buffers(d, slot, need);
+        if (rc != AGCN_OK) return rc;
+    }
+    const int b = d->pbuf_next[slot];
+    d->pbuf_next[slot] ^= 1;
+    const int64_t slice_rows = d->layout.rows_per_chunk;
+    const size_t bytes = (size_t)slice_rows * dim * sizeof(float);
+    for (int c = 0; c < d->chunks; c++) {
+        const float *src = d_x_block + (int64_t)c * slice_rows * dim;
+        const int64_t dst_row = (int64_t)c * d->world * slice_rows + (int64_t)d->rank * slice_rows;
+        for (int i = 0; i < d->world; i++) {
+            const int r = (d->rank + i) % d->world;          // every rank starts with a different peer
+            AGCN_CUDA(cudaMemcpyAsync(d->pbuf_peer[slot][b][r] + dst_row * dim, src, bytes, cudaMemcpyDefault, d->s_comm));
+        }
+        int rc = dist_barrier(d);
+        if (rc != AGCN_OK) return rc;
+        AGCN_CUDA(cudaEventRecord(d->ev_ready[slot][c], d->s_comm));
+    }
+    d->gathered_ptr[slot] = d->pbuf[slot][b];
+    return AGCN_OK;
+}
+
 static int dist_gather_begin(agcn_dist *d, int slot, const float *d_x_block, int dim, cudaStream_t s)
 {
     AGCN_REQUIRE(d != nullptr && (d->plan != nullptr || d->tiled != nullptr), "agcn_dist_gather_begin: no graph set");
@@ -264,6 +372,14 @@ static int dist_gather_begin(agcn_dist *d, int slot, const float *d_x_block, int
     }
     AGCN_REQUIRE(d->comm != nullptr, "agcn_dist_gather_begin: the context was created without a communicator (id = NULL): "
                                      "exchange the operand yourself and call agcn_dist_spmm_on_gathered");
+    if (d->push) {
+        AGCN_CUDA(cudaEventRecord(d->ev_input, s));
+        AGCN_CUDA(cudaStreamWaitEvent(d->s_comm, d->ev_input, 0));
+        int rc = dist_push(d, slot, d_x_block, dim);
+        if (rc != AGCN_OK) return rc;
+        d->slot_used[slot] = true;
+        return AGCN_OK;
+    }
     const size_t need = (size_t)d->n_gathered * dim * sizeof(float);
     if (need > d->gathered_cap[slot]) {
         if (d->gathered[slot] != nullptr) AGCN_CUDA(cudaFree(d->gathered[slot]));
@@ -418,6 +534,16 @@ extern "C" int agcn_dist_spmm_gathered(agcn_dist *dist, int slot, float *d_y_blo
 {
     agcn::clear_error();
     return agcn::dist_spmm_gathered(dist, slot, d_y_block, dim, activation, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int agcn_dist_wait_gathered(agcn_dist *dist, int slot, void *stream)
+{
+    using namespace agcn;
+    clear_error();
+    AGCN_REQUIRE(dist != nullptr && slot >= 0 && slot < DIST_SLOTS && dist->slot_used[slot], "agcn_dist_wait_gathered: empty slot");
+    const int n = dist->world == 1 ? 1 : dist->chunks;
+    for (int c = 0; c < n; c++) AGCN_CUDA(cudaStreamWaitEvent(static_cast<cudaStream_t>(stream), dist->ev_ready[slot][c], 0));
+    return AGCN_OK;
 }
 
 extern "C" int agcn_dist_spmm_step(agcn_dist *dist, const float *d_x_block, float *d_y_block, int dim, int activation,

@@ -314,7 +314,15 @@ int agcn_spmm_host_batch(agcn_host_ctx *ctx, const int32_t *h_block4, int64_t n_
  * each other can have their exchanges started together.  agcn_dist_spmm_step
  * is both calls on slot 0.  With world = 1 nothing is exchanged and the block
  * is read in place (it must stay valid until the product has run).  All calls
- * are asynchronous; every rank must issue the same sequence of exchanges.
+ * are asynchronous; every rank must issue the same sequence of exchanges, and a
+ * slot's product must be enqueued before the slot's next exchange is begun.
+ *
+ * The exchange itself is ncclAllGather by default.  With the environment
+ * variable AGCN_DIST_EXCHANGE=push (read by agcn_dist_create) every rank instead
+ * copies its block straight into every peer's gathered buffer with the copy
+ * engines (CUDA IPC mappings of buffers the library allocates, peer copies over
+ * NVLink, no SM is taken from the products running beside it) and a one-float
+ * all-reduce marks the arrival; all ranks must then be processes on one node.
  * ---------------------------------------------------------------------- */
 #define AGCN_MAX_WORLD      64
 #define AGCN_DIST_ID_BYTES 128
@@ -344,6 +352,8 @@ int agcn_dist_spmm_gathered(agcn_dist *dist, int slot, float *d_y_block, int dim
                             void *stream);
 int agcn_dist_spmm_step(agcn_dist *dist, const float *d_x_block, float *d_y_block, int dim,
                         int activation, void *stream);
+/* makes `stream` wait for the whole exchange of a slot without multiplying (timing the exchange alone) */
+int agcn_dist_wait_gathered(agcn_dist *dist, int slot, void *stream);
 /* Y_block = act(A_block * X) on an operand the caller assembled itself: d_gathered is
  * [world * rows_per_block x dim], rank g's block rows at rows g * rows_per_block ... (with
  * exchange_slices > 1: slice c of every rank first, as agcn_dist_gather_begin lays it out). */
