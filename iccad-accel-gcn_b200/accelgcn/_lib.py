@@ -41,6 +41,7 @@ PROTOTYPES = {
     "agcn_spmm_host": (_int, [_vp, _vp, _i64, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int]),
     "agcn_host_spmm_batch": (_int, [_vp, _int, _vp, _vp, _vp]),
     "agcn_spmm_host_batch": (_int, [_vp, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _int, _vp, _vp, _vp]),
+    "agcn_host_last_timing": (_int, [_vp, _vp]),
     "agcn_spmm_tiled_create": (_int, [ctypes.POINTER(_vp), _vp, _vp, _vp, _i64, _i64, _i64, _vp, _int, _vp]),
     "agcn_spmm_tiled_run": (_int, [_vp, _vp, _i64, _vp, _i64, _int, _int, _vp]),
     "agcn_spmm_tiled_run_range": (_int, [_vp, _int, _vp, _i64, _vp, _i64, _int, _int, _vp]),

@@ -248,6 +248,13 @@ class HostSpmm:
                                                   n_rows, n_cols, _numel(indices), n, px, py, dims))
         return ys
 
+    def last_timing(self) -> dict:
+        """Milliseconds of the last streamed step_batch call, from the start of its uploads (agcn_host_last_timing)."""
+        ms = (ctypes.c_float * 6)()
+        _lib.check(self._lib.agcn_host_last_timing(self._h, ms))
+        keys = ("a_uploaded", "first_kernel_started", "last_kernel_finished", "last_y_downloaded", "host_plan_built", "host_all_enqueued")
+        return dict(zip(keys, (float(v) for v in ms)))
+
     def __call__(self, block4, indices, vals, x, n_rows: int, out=None):
         n_cols, dim = x.shape
         y = out if out is not None else np.empty((n_rows, dim), dtype=np.float32)

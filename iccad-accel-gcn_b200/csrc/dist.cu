@@ -79,6 +79,7 @@ static int nccl_api(const NcclApi **out)
 
 constexpr int DIST_SLOTS = 4;             // gathered operands that can be in flight at once
 constexpr int DIST_MAX_CHUNKS = 16;
+constexpr int DIST_COPY_STREAMS = 4;
 
 }  // namespace agcn
 
@@ -111,6 +112,9 @@ struct agcn_dist {
     float *pbuf_peer[agcn::DIST_SLOTS][2][agcn::DIST_MAX_WORLD] = {};   // the same buffers of every rank, mapped here
     size_t pbuf_cap[agcn::DIST_SLOTS] = {};
     int pbuf_next[agcn::DIST_SLOTS] = {};
+    cudaStream_t s_copy[agcn::DIST_COPY_STREAMS] = {};                   // the pushes run on several streams (several copy engines)
+    cudaEvent_t ev_copy[agcn::DIST_COPY_STREAMS] = {};
+    cudaEvent_t ev_fork = nullptr;
     float *d_token = nullptr;                                           // one float: operand of the barrier all-reduce
     unsigned char *d_handles = nullptr;                                 // [world][64]: exchange of IPC handles
 };
@@ -150,6 +154,11 @@ static void dist_free(agcn_dist *d)
                 if (r != d->rank && d->pbuf_peer[s][b][r] != nullptr) cudaIpcCloseMemHandle(d->pbuf_peer[s][b][r]);
             cudaFree(d->pbuf[s][b]);
         }
+    for (int i = 0; i < DIST_COPY_STREAMS; i++) {
+        if (d->s_copy[i]) cudaStreamDestroy(d->s_copy[i]);
+        if (d->ev_copy[i]) cudaEventDestroy(d->ev_copy[i]);
+    }
+    if (d->ev_fork) cudaEventDestroy(d->ev_fork);
     cudaFree(d->d_token);
     cudaFree(d->d_handles);
     if (d->comm != nullptr && d->nccl != nullptr) d->nccl->CommDestroy(d->comm);
@@ -184,6 +193,11 @@ static int dist_create(agcn_dist **out, int rank, int world, const void *id)
         AGCN_CUDA(cudaMalloc(&d->d_token, sizeof(float)));
         AGCN_CUDA(cudaMemset(d->d_token, 0, sizeof(float)));
         AGCN_CUDA(cudaMalloc(&d->d_handles, (size_t)world * sizeof(cudaIpcMemHandle_t)));
+        for (int i = 0; i < DIST_COPY_STREAMS; i++) {
+            AGCN_CUDA(cudaStreamCreateWithFlags(&d->s_copy[i], cudaStreamNonBlocking));
+            AGCN_CUDA(cudaEventCreateWithFlags(&d->ev_copy[i], cudaEventDisableTiming));
+        }
+        AGCN_CUDA(cudaEventCreateWithFlags(&d->ev_fork, cudaEventDisableTiming));
     }
     guard.d = nullptr;
     *out = d;
@@ -342,13 +356,27 @@ static int dist_push(agcn_dist *d, int slot, const float *d_x_block, int dim)
     const int b = d->pbuf_next[slot];
     d->pbuf_next[slot] ^= 1;
     const int64_t slice_rows = d->layout.rows_per_chunk;
-    const size_t bytes = (size_t)slice_rows * dim * sizeof(float);
+    // each peer's copy is cut in two and the pieces are dealt over the copy streams, so that several
+    // copy engines work at once; the communication stream forks into them and joins before the barrier
+    const int64_t half_rows = (slice_rows + 1) / 2;
     for (int c = 0; c < d->chunks; c++) {
         const float *src = d_x_block + (int64_t)c * slice_rows * dim;
         const int64_t dst_row = (int64_t)c * d->world * slice_rows + (int64_t)d->rank * slice_rows;
+        AGCN_CUDA(cudaEventRecord(d->ev_fork, d->s_comm));
+        for (int i = 0; i < DIST_COPY_STREAMS; i++) AGCN_CUDA(cudaStreamWaitEvent(d->s_copy[i], d->ev_fork, 0));
+        int piece = 0;
         for (int i = 0; i < d->world; i++) {
             const int r = (d->rank + i) % d->world;          // every rank starts with a different peer
-            AGCN_CUDA(cudaMemcpyAsync(d->pbuf_peer[slot][b][r] + dst_row * dim, src, bytes, cudaMemcpyDefault, d->s_comm));
+            for (int h = 0; h < 2; h++, piece++) {
+                const int64_t r0 = h * half_rows, r1 = h == 0 ? half_rows : slice_rows;
+                if (r1 <= r0) continue;
+                AGCN_CUDA(cudaMemcpyAsync(d->pbuf_peer[slot][b][r] + (dst_row + r0) * dim, src + r0 * dim,
+                                          (size_t)(r1 - r0) * dim * sizeof(float), cudaMemcpyDefault, d->s_copy[piece % DIST_COPY_STREAMS]));
+            }
+        }
+        for (int i = 0; i < DIST_COPY_STREAMS; i++) {
+            AGCN_CUDA(cudaEventRecord(d->ev_copy[i], d->s_copy[i]));
+            AGCN_CUDA(cudaStreamWaitEvent(d->s_comm, d->ev_copy[i], 0));
         }
         int rc = dist_barrier(d);
         if (rc != AGCN_OK) return rc;

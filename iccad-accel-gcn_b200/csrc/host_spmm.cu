@@ -17,6 +17,7 @@
 #include "internal.h"
 
 #include <algorithm>
+#include <chrono>
 #include <new>
 #include <vector>
 
@@ -39,6 +40,10 @@ struct agcn_host_ctx {
     int *d_abort = nullptr;                           // device word: set when a column id is out of range
     std::vector<cudaEvent_t> events;
     size_t events_used = 0;
+    // timing of the last agcn_spmm_host_batch call (agcn_host_last_timing)
+    cudaEvent_t t_up0 = nullptr, t_up1 = nullptr, t_run0 = nullptr, t_run1 = nullptr, t_down1 = nullptr;
+    float host_plan_ms = 0.f, host_enqueue_ms = 0.f;
+    bool timed = false;
 };
 
 namespace agcn {
@@ -287,10 +292,14 @@ static int host_graph_and_products(agcn_host_ctx *c, const int *h_block4, int64_
         rc = host_set_graph(c, h_block4, n_blocks, h_indices, h_vals, n_rows, n_cols, nnz);
         return rc != AGCN_OK ? rc : host_products(c, n, h_x, h_y, dims);
     }
+    const auto host_t0 = std::chrono::steady_clock::now();
+    c->timed = false;
+    AGCN_CUDA(cudaEventRecord(c->t_up0, c->s_up));
     rc = upload_block4_and_plan(c, h_block4, n_blocks, n_rows, n_cols, nnz);
     if (rc != AGCN_OK) return rc;
     rc = reserve_products(c, n, dims, true);
     if (rc != AGCN_OK) return rc;
+    const auto host_t1 = std::chrono::steady_clock::now();
     // ranges of about 32 MB of (column id, value) pairs: long enough for full PCIe speed, short
     // enough that the first product starts early and the last download is short
     plan_parts(c, h_block4, (int)std::max<int64_t>(1, std::min<int64_t>(64, (nnz * 8) >> 25)));
@@ -303,7 +312,9 @@ static int host_graph_and_products(agcn_host_ctx *c, const int *h_block4, int64_
         const int64_t p0 = c->part_loc[k], p1 = c->part_loc[k + 1];
         AGCN_CUDA(cudaMemcpyAsync(idx + p0, h_indices + p0, (size_t)(p1 - p0) * 4, cudaMemcpyHostToDevice, c->s_up));
         AGCN_CUDA(cudaMemcpyAsync(val + p0, h_vals + p0, (size_t)(p1 - p0) * 4, cudaMemcpyHostToDevice, c->s_up));
+        if (k == n_parts - 1) AGCN_CUDA(cudaEventRecord(c->t_up1, c->s_up));
         rc = ctx_chain(c, c->s_up, c->s_run);
+        if (k == 0) AGCN_CUDA(cudaEventRecord(c->t_run0, c->s_run));
         // a column id outside [0, n_cols) sets the abort word, and every kernel behind it returns at once
         if (rc == AGCN_OK) rc = spmm_check_cols(idx + p0, p1 - p0, n_cols, c->d_abort, c->s_run);
         for (int i = 0; i < n && rc == AGCN_OK; i++) {
@@ -327,8 +338,12 @@ static int host_graph_and_products(agcn_host_ctx *c, const int *h_block4, int64_
                                static_cast<float *>(c->ybuf[i]), dims[i], dims[i], c->s_run, 0, 0, tail);
         if (rc != AGCN_OK) { ctx_sync(c); return rc; }
     }
+    AGCN_CUDA(cudaEventRecord(c->t_run1, c->s_run));
     rc = ctx_chain(c, c->s_run, c->s_down);
     for (int i = 0; i < n && rc == AGCN_OK; i++) rc = download_rows(c, i, h_y[i], dims[i], c->first_deferred_row, n_rows);
+    AGCN_CUDA(cudaEventRecord(c->t_down1, c->s_down));
+    c->host_plan_ms = std::chrono::duration<float, std::milli>(host_t1 - host_t0).count();
+    c->host_enqueue_ms = std::chrono::duration<float, std::milli>(std::chrono::steady_clock::now() - host_t0).count();
     int bad = 0;
     if (rc == AGCN_OK && cudaMemcpyAsync(&bad, c->d_abort, sizeof(int), cudaMemcpyDeviceToHost, c->s_run) != cudaSuccess) rc = AGCN_ERR_CUDA;
     const int rc_sync = ctx_sync(c);
@@ -340,6 +355,7 @@ static int host_graph_and_products(agcn_host_ctx *c, const int *h_block4, int64_
         return AGCN_ERR_RANGE;
     }
     plan_parts(c, h_block4, 4);         // later agcn_host_spmm calls on this graph use a few large ranges
+    c->timed = true;
     return AGCN_OK;
 }
 
@@ -356,6 +372,8 @@ extern "C" int agcn_host_ctx_create(agcn_host_ctx **ctx)
     cudaError_t e = cudaStreamCreateWithFlags(&c->s_up, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&c->s_run, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&c->s_down, cudaStreamNonBlocking);
+    for (cudaEvent_t *ev : {&c->t_up0, &c->t_up1, &c->t_run0, &c->t_run1, &c->t_down1})
+        if (e == cudaSuccess) e = cudaEventCreate(ev);
     if (e != cudaSuccess) {
         agcn_host_ctx_destroy(c);
         set_error("agcn_host_ctx_create: cudaStreamCreate: %s", cudaGetErrorString(e));
@@ -376,6 +394,7 @@ extern "C" int agcn_host_ctx_destroy(agcn_host_ctx *ctx)
     for (void *p : ctx->cbuf) cudaFree(p);
     cudaFree(ctx->d_abort);
     for (cudaEvent_t e : ctx->events) cudaEventDestroy(e);
+    for (cudaEvent_t e : {ctx->t_up0, ctx->t_up1, ctx->t_run0, ctx->t_run1, ctx->t_down1}) if (e) cudaEventDestroy(e);
     if (ctx->s_up) cudaStreamDestroy(ctx->s_up);
     if (ctx->s_run) cudaStreamDestroy(ctx->s_run);
     if (ctx->s_down) cudaStreamDestroy(ctx->s_down);
@@ -419,4 +438,23 @@ extern "C" int agcn_spmm_host_batch(agcn_host_ctx *ctx, const int32_t *h_block4,
 {
     agcn::clear_error();
     return agcn::host_graph_and_products(ctx, h_block4, n_blocks, h_indices, h_vals, n_rows, n_cols, nnz, n_products, h_x, h_y, dims);
+}
+
+// Where the time of the last agcn_spmm_host_batch call on this context went, in milliseconds from
+// the start of its uploads: [0] last byte of A uploaded, [1] first kernel started, [2] last kernel
+// finished, [3] last byte of Y downloaded; then host-side times: [4] until the plan was built,
+// [5] until everything was enqueued.
+extern "C" int agcn_host_last_timing(agcn_host_ctx *ctx, float *ms6)
+{
+    using namespace agcn;
+    clear_error();
+    AGCN_REQUIRE(ctx != nullptr && ms6 != nullptr, "agcn_host_last_timing: null argument");
+    AGCN_REQUIRE(ctx->timed, "agcn_host_last_timing: no streamed agcn_spmm_host_batch call has completed on this context");
+    AGCN_CUDA(cudaEventElapsedTime(&ms6[0], ctx->t_up0, ctx->t_up1));
+    AGCN_CUDA(cudaEventElapsedTime(&ms6[1], ctx->t_up0, ctx->t_run0));
+    AGCN_CUDA(cudaEventElapsedTime(&ms6[2], ctx->t_up0, ctx->t_run1));
+    AGCN_CUDA(cudaEventElapsedTime(&ms6[3], ctx->t_up0, ctx->t_down1));
+    ms6[4] = ctx->host_plan_ms;
+    ms6[5] = ctx->host_enqueue_ms;
+    return AGCN_OK;
 }

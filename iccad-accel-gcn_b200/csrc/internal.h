@@ -14,6 +14,7 @@ struct agcn_spmm_plan {
     int l2_bytes = 0, sm_count = 0;   // of the device the plan was created on
     int panel_override = 0;           // AGCN_SPMM_PANEL at creation (0 = choose automatically)
     bool never_split = false;         // set for the ranges of a column-tiled product
+    int batch_override = 0;           // AGCN_SPMM_BATCH at creation: 8 or 16 gathers in flight per lane (experiments)
     int pad_unaligned = 1;            // AGCN_SPMM_PAD at creation: copy unaligned X into 16-byte-aligned rows
     float *x_pad = nullptr;           // [n_cols][dim rounded up to 4], grown on demand
     size_t x_pad_bytes = 0;

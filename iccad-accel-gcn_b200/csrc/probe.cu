@@ -12,17 +12,13 @@
 
 namespace agcn {
 
-__device__ __forceinline__ uint32_t probe_hash(uint32_t x)
-{
-    x ^= x >> 16; x *= 0x7feb352du;
-    x ^= x >> 15; x *= 0x846ca68bu;
-    x ^= x >> 16;
-    return x;
-}
+// row number of the k-th gather of a warp: multiplicative (Fibonacci) hashing, one multiply and one
+// shift, so that the probe spends its instructions on loads (the table has a power-of-two row count)
+__device__ __forceinline__ uint32_t probe_row(uint32_t k, int shift) { return (k * 0x9E3779B1u) >> shift; }
 
 template <int S>
 __global__ void __launch_bounds__(256)
-probe_gather_kernel(const float *__restrict__ table, uint32_t table_rows, int row_floats, int rows_per_warp, float *__restrict__ sink)
+probe_gather_kernel(const float *__restrict__ table, int row_shift, int row_floats, int rows_per_warp, float *__restrict__ sink)
 {
     constexpr int NS = 32 / S;
     const int lane = lane_id(), slot = lane / S, col = (lane % S) * 4;
@@ -34,7 +30,7 @@ probe_gather_kernel(const float *__restrict__ table, uint32_t table_rows, int ro
         float4 v[4];
 #pragma unroll
         for (int u = 0; u < 4; u++) {
-            const uint32_t r = probe_hash(warp * 0x9e3779b9u + (uint32_t)(i + u * NS)) % table_rows;
+            const uint32_t r = probe_row(warp * (uint32_t)rows_per_warp + (uint32_t)(i + u * NS), row_shift);
             v[u] = ld_x4(base + (int64_t)r * row_floats, pol.keep);
         }
 #pragma unroll
@@ -46,7 +42,7 @@ probe_gather_kernel(const float *__restrict__ table, uint32_t table_rows, int ro
 
 }  // namespace agcn
 
-// table_rows rows of row_floats floats (32, 64 or 128: 128 / 256 / 512-byte rows); total_rows rows
+// table_rows (a power of two) rows of row_floats floats (32, 64 or 128: 128 / 256 / 512-byte rows); total_rows rows
 // are gathered per launch; the rate over `iters` launches (after one warm-up) is returned in GB/s.
 extern "C" int agcn_probe_gather_bandwidth(int64_t table_rows, int row_floats, int64_t total_rows, int iters,
                                            int resident_blocks, double *gb_per_s)
@@ -55,8 +51,10 @@ extern "C" int agcn_probe_gather_bandwidth(int64_t table_rows, int row_floats, i
     clear_error();
     AGCN_REQUIRE(gb_per_s != nullptr, "agcn_probe_gather_bandwidth: null result pointer");
     AGCN_REQUIRE(row_floats == 32 || row_floats == 64 || row_floats == 128, "agcn_probe_gather_bandwidth: row_floats must be 32, 64 or 128");
-    AGCN_REQUIRE(table_rows > 0 && table_rows < ((int64_t)1 << 31) && total_rows > 0 && iters >= 1,
-                 "agcn_probe_gather_bandwidth: bad sizes");
+    AGCN_REQUIRE(table_rows >= 2 && table_rows <= ((int64_t)1 << 30) && (table_rows & (table_rows - 1)) == 0 && total_rows > 0 && iters >= 1,
+                 "agcn_probe_gather_bandwidth: table_rows must be a power of two, 2..2^30");
+    int row_shift = 32;
+    while (((int64_t)1 << (32 - row_shift)) < table_rows) row_shift--;
     AGCN_REQUIRE(resident_blocks >= 0 && resident_blocks <= 8, "agcn_probe_gather_bandwidth: resident_blocks must be 0..8");
     const int rows_per_warp = 512;       // short warps, many of them: the grid must fill every SM several times over
     const int64_t warps = ceil_div(total_rows, rows_per_warp);
@@ -78,9 +76,9 @@ extern "C" int agcn_probe_gather_bandwidth(int64_t table_rows, int row_floats, i
         AGCN_CUDA(cudaFuncSetAttribute(probe_gather_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     }
     auto launch = [&]() {
-        if (row_floats == 32) probe_gather_kernel<8><<<grid, 256, smem>>>(table, (uint32_t)table_rows, row_floats, rows_per_warp, sink);
-        else if (row_floats == 64) probe_gather_kernel<16><<<grid, 256, smem>>>(table, (uint32_t)table_rows, row_floats, rows_per_warp, sink);
-        else probe_gather_kernel<32><<<grid, 256, smem>>>(table, (uint32_t)table_rows, row_floats, rows_per_warp, sink);
+        if (row_floats == 32) probe_gather_kernel<8><<<grid, 256, smem>>>(table, row_shift, row_floats, rows_per_warp, sink);
+        else if (row_floats == 64) probe_gather_kernel<16><<<grid, 256, smem>>>(table, row_shift, row_floats, rows_per_warp, sink);
+        else probe_gather_kernel<32><<<grid, 256, smem>>>(table, row_shift, row_floats, rows_per_warp, sink);
     };
     launch();                                             // warm-up: brings the table into L2
     cudaError_t e = cudaGetLastError();

@@ -112,6 +112,7 @@ int spmm_create(agcn_spmm_plan **out, const int *d_block4, int64_t n_blocks, con
         cudaDeviceGetAttribute(&p->sm_count, cudaDevAttrMultiProcessorCount, dev);
         p->panel_override = env_int("AGCN_SPMM_PANEL", 0);
         p->pad_unaligned = env_int("AGCN_SPMM_PAD", 1);
+        p->batch_override = env_int("AGCN_SPMM_BATCH", 0);
     }
     *out = p;
     return AGCN_OK;
@@ -128,9 +129,14 @@ int spmm_check_cols(const int *d_idx, int64_t count, int64_t n_cols, int *d_flag
 }
 
 template <int S>
-static void launch_units(const SpmmParams &prm, unsigned grid, bool small_launch, bool plain, cudaStream_t s)
+static void launch_units(const SpmmParams &prm, unsigned grid, bool small_launch, bool plain, int batch, cudaStream_t s)
 {
-    if (small_launch) {
+    if (batch == 8) {          // experiment knob AGCN_SPMM_BATCH=8: 8 gathers in flight per lane at 3 thread blocks per SM
+        if (plain) { auto k = spmm_units_kernel<S, 8, 3, true>; AGCN_KERNEL(k, grid, SPMM_THREADS, s, prm); }
+        else { auto k = spmm_units_kernel<S, 8, 3, false>; AGCN_KERNEL(k, grid, SPMM_THREADS, s, prm); }
+        return;
+    }
+    if (small_launch || batch == 16) {
         if (plain) { auto k = spmm_units_kernel<S, SPMM_SMALL_GATHER_BATCH, SPMM_SMALL_MIN_BLOCKS, true>; AGCN_KERNEL(k, grid, SPMM_THREADS, s, prm); }
         else { auto k = spmm_units_kernel<S, SPMM_SMALL_GATHER_BATCH, SPMM_SMALL_MIN_BLOCKS, false>; AGCN_KERNEL(k, grid, SPMM_THREADS, s, prm); }
     } else {
@@ -140,13 +146,13 @@ static void launch_units(const SpmmParams &prm, unsigned grid, bool small_launch
 }
 
 static void launch_units_for_width(int width, bool vec, const SpmmParams &prm, unsigned grid, bool small_launch, bool plain,
-                                   cudaStream_t s)
+                                   int batch, cudaStream_t s)
 {
-    if (!vec) launch_units<0>(prm, grid, small_launch, plain, s);
-    else if (width <= 16) launch_units<4>(prm, grid, small_launch, plain, s);
-    else if (width <= 32) launch_units<8>(prm, grid, small_launch, plain, s);
-    else if (width <= 64) launch_units<16>(prm, grid, small_launch, plain, s);
-    else launch_units<32>(prm, grid, small_launch, plain, s);
+    if (!vec) launch_units<0>(prm, grid, small_launch, plain, batch, s);
+    else if (width <= 16) launch_units<4>(prm, grid, small_launch, plain, batch, s);
+    else if (width <= 32) launch_units<8>(prm, grid, small_launch, plain, batch, s);
+    else if (width <= 64) launch_units<16>(prm, grid, small_launch, plain, batch, s);
+    else launch_units<32>(prm, grid, small_launch, plain, batch, s);
 }
 
 // Rows of X that are not 16-byte aligned (dim % 4 != 0 with the reference's ld = dim, an odd
@@ -228,12 +234,10 @@ int spmm_run_prepared(agcn_spmm_plan *p, const int *d_indices, const float *d_va
     }
     if (p->panel_override > 0) panel = p->panel_override;
     const bool whole = unit0 == 0 && unit1 == p->n_units && part.carry;
-    if (!whole) {
-        // the carry scratch holds the partial sums of ONE column panel between the unit launches and
-        // the carry kernel: a product issued in parts therefore runs as a single panel
-        AGCN_REQUIRE(dim <= SPMM_PANEL, "agcn_spmm_run: a product issued in unit ranges is limited to %d columns", SPMM_PANEL);
-        panel = SPMM_PANEL;
-    }
+    // A carry slot holds SPMM_PANEL floats and every column pass uses its own columns of it, so a
+    // product of up to SPMM_PANEL columns can be issued in parts (unit launches now, carry kernel
+    // later) whatever its passes are -- with the same passes, hence the same bits, as a whole run.
+    if (!whole) AGCN_REQUIRE(dim <= SPMM_PANEL, "agcn_spmm_run: a product issued in unit ranges is limited to %d columns", SPMM_PANEL);
     AGCN_REQUIRE(panel >= 1 && panel <= SPMM_PANEL, "agcn_spmm_run: AGCN_SPMM_PANEL must be 1..%d", SPMM_PANEL);
     if (x_vec && panel % 4 != 0) panel = (panel + 3) & ~3;         // keep every panel's first column 16-byte aligned
     if (panel > SPMM_PANEL) panel = SPMM_PANEL;
@@ -245,7 +249,8 @@ int spmm_run_prepared(agcn_spmm_plan *p, const int *d_indices, const float *d_va
         prm.idx = d_indices; prm.val = d_vals;
         prm.x = x_use + col0; prm.ldx = ldx_use;
         prm.y = d_y + col0; prm.ldy = ldy;
-        prm.unit_carry = p->unit_carry; prm.carry = part.carry_buf != nullptr ? part.carry_buf : p->carry;
+        prm.unit_carry = p->unit_carry;
+        prm.carry = (part.carry_buf != nullptr ? part.carry_buf : p->carry) + col0 % SPMM_PANEL;
         prm.zero_rows = p->zero_rows; prm.n_zero_rows = p->n_zero;
         prm.relu = activation;
         prm.accumulate = accumulate;
@@ -256,7 +261,7 @@ int spmm_run_prepared(agcn_spmm_plan *p, const int *d_indices, const float *d_va
         prm.dim = vec ? (width + 3) & ~3 : width;       // columns gathered (the padded copy holds zeros past dim)
         const bool plain = !accumulate && (vec ? y_vec : true);
         if (grid > 0) {
-            launch_units_for_width(prm.dim, vec, prm, (unsigned)grid, small_launch, plain, s);
+            launch_units_for_width(prm.dim, vec, prm, (unsigned)grid, small_launch, plain, p->batch_override, s);
             AGCN_LAUNCH_CHECK("spmm_units_kernel");
             p->launches_last_run++;
         }

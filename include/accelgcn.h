@@ -277,6 +277,12 @@ int agcn_spmm_host_batch(agcn_host_ctx *ctx, const int32_t *h_block4, int64_t n_
                          int64_t n_rows, int64_t n_cols, int64_t nnz,
                          int n_products, const float *const *h_x, float *const *h_y, const int *dims);
 
+/* Where the time of the last agcn_spmm_host_batch call on this context went (the streamed form:
+ * every width a multiple of 4 up to 128), in milliseconds from the start of its uploads:
+ * ms6[0] last byte of A uploaded, [1] first kernel started, [2] last kernel finished, [3] last
+ * byte of Y downloaded; host side: [4] until the plan was built, [5] until all was enqueued. */
+int agcn_host_last_timing(agcn_host_ctx *ctx, float *ms6);
+
 /* ------------------------------------------------------------------------
  * Row-sharded multi-GPU SpMM.  The reference is single-GPU (main.cu:53-182);
  * this applies its operator block by block, one caller (process or thread) per
@@ -385,7 +391,8 @@ int agcn_gcn2_forward_destroy(agcn_gcn2 *fwd);
  * GPU gathers whole rows of an L2-resident table with the access shape of the
  * SpMM (16-byte lanes, four rows in flight per lane, same residency and L2
  * policy, a chosen number of resident thread blocks per SM) -- the ceiling of a gather SpMM on graphs dense enough that X is
- * re-read from L2 rather than from HBM.  row_floats is 32, 64 or 128.
+ * re-read from L2 rather than from HBM.  row_floats is 32, 64 or 128; table_rows
+ * is a power of two.
  * ---------------------------------------------------------------------- */
 int agcn_probe_gather_bandwidth(int64_t table_rows, int row_floats, int64_t total_rows, int iters,
                                 int resident_blocks /* per SM; 0 = no limit, the SpMM keeps 5 */,
