@@ -59,7 +59,8 @@ METRIC, UNIT = "spmm_gflops", "GFLOP/s"
 FALLBACK_HBM_GBS = 6650.0
 # (workload, dim, kernel variant) -> dram__bytes_read + dram__bytes_write per product, from the ncu captures
 # summarised under profiles/ (same command as the default run)
-NCU_TRAFFIC_BYTES = {("cfg2", 128, "two 64-column passes"): 4.070e9}
+NCU_TRAFFIC_BYTES = {("cfg2", 128, "column-tiled"): 1.770e9, ("cfg2", 128, "two 64-column passes"): 3.971e9,
+                     ("cfg3", 64, "one pass"): 9.524e9}
 
 
 def hbm_peak():
