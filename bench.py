@@ -843,7 +843,7 @@ def ours_gcn(args, rank, world, local_rank):
         # CPU baseline on a bounded sample: every k-th row of A (SpMM) and of H (X*W, numpy/BLAS)
         from oracle import oracle
         ix_h, v_h = ix_keep.cpu().numpy(), v_keep.cpu().numpy()
-        x_h = shard.from_blocks([x_block]).cpu().numpy()
+        x_h = x_block[:n].cpu().numpy()           # one rank: block rows are the matrix rows
         gf, dt, desc, stride = cpu_spmm_rate(ip_h, ix_h, v_h, [x_h], args.cpu_seconds)
         rows = x_h[::stride]
         t0 = time.perf_counter()
