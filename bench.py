@@ -390,6 +390,18 @@ def ours(args, rank, world, local_rank):
         shard_sliced = sharded.ShardedSpmm(ip, ix, v, rank, world, exchange_slices=args.slices)
         assert shard_sliced.rows_per_block == shard.rows_per_block, "--slices must divide the block height"
         shard_of.update({d: shard_sliced for d in dims if d >= args.slices_min_dim})
+    elif world > 1 and args.tiled != "off":
+        # a gathered operand that does not fit L2 is multiplied column range by column range (as on one GPU):
+        # widths that want the same number of ranges share one more context of the same layout
+        lib = _lib.load()
+        by_ranges = {}
+        for d in dims:
+            k = lib.agcn_spmm_tiled_suggest(shard.rows_per_block, shard.n_gathered, shard.local_nnz, d)
+            if k > 1:
+                by_ranges.setdefault(k, []).append(d)
+        for k, ds in by_ranges.items():
+            tiled_shard = sharded.ShardedSpmm(ip, ix, v, rank, world, column_ranges=k)
+            shard_of.update({d: tiled_shard for d in ds})
     per = shard.rows_per_block
     n_blocks_local = int(shard.n_blocks)
     nb = torch.tensor([n_blocks_local], dtype=torch.int64, device=dev)
@@ -514,9 +526,10 @@ def ours(args, rank, world, local_rank):
         nnz_local = torch.tensor([shard.local_nnz], dtype=torch.float64, device=dev)
         nnz_max = nnz_local.clone(); dist.all_reduce(nnz_max, op=dist.ReduceOp.MAX)
         multi = {"step_ms": total_ms / args.steps, "products_without_exchange_ms": compute_ms,
-                 "exchanges_without_products_ms": exchange_ms, "exchange": os.environ.get("AGCN_DIST_EXCHANGE", "nccl all-gather"),
+                 "exchanges_without_products_ms": exchange_ms, "exchange": "ncclAllGather inside the library",
                  "step_minus_products_ms": total_ms / args.steps - compute_ms,
                  "exchange_slices": {str(d): shard_of[d].slices for d in dims},
+                 "column_ranges": {str(d): (1 if shard_of[d] is shard else "tiled") for d in dims},
                  "rows_per_block": per, "max_local_nnz_over_mean": float(nnz_max.item()) * world / nnz,
                  "exchanged_bytes_in_per_rank_per_step": 4 * sum(dims) * per * (world - 1),
                  "limiting_phase": "products" if compute_ms > 0.5 * total_ms / args.steps else "exchange"}

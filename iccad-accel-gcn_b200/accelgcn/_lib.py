@@ -54,7 +54,7 @@ PROTOTYPES = {
     "agcn_dist_unique_id": (_int, [_vp]),
     "agcn_dist_create": (_int, [ctypes.POINTER(_vp), _int, _int, _vp]),
     "agcn_dist_destroy": (_int, [_vp]),
-    "agcn_dist_set_graph": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _int, _vp]),
+    "agcn_dist_set_graph": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _int, _int, _vp]),
     "agcn_dist_info": (_int, [_vp, ctypes.POINTER(_i64), ctypes.POINTER(_i64), ctypes.POINTER(_i64),
                              ctypes.POINTER(_i64), ctypes.POINTER(_int), ctypes.POINTER(_int)]),
     "agcn_dist_block_rows": (_int, [_vp, _int, _vp, _vp]),

@@ -90,12 +90,13 @@ class ShardedSpmm:
     indptr / indices / vals are the WHOLE degree-ordered matrix as CUDA tensors on this rank's
     device (every rank builds the same synthetic matrix from the same seed, or loads the same
     files); the block is cut out inside the library.  `exchange_slices` > 1 exchanges the dense
-    operand in that many row slices and starts the product over a slice when it has arrived.
+    operand in that many row slices and starts the product over a slice when it has arrived;
+    `column_ranges` > 1 (with one slice) tiles the block's columns for a gathered operand larger than L2.
     `communicator=False` builds the block without NCCL (the caller assembles the gathered operand
     itself and calls `multiply_gathered`): used to run every rank's block in one process."""
 
     def __init__(self, indptr, indices, vals, rank: int, world_size: int, group=None, exchange_slices: int = 1,
-                 communicator: bool = True):
+                 communicator: bool = True, column_ranges: int = 1):
         import torch
         self._torch = torch
         self._lib = lib = _lib.load()
@@ -109,7 +110,7 @@ class ShardedSpmm:
             self._h = h
             s = torch.cuda.current_stream(self.device)
             _lib.check(lib.agcn_dist_set_graph(h, indptr.data_ptr(), indices.data_ptr(), vals.data_ptr(), self.n,
-                                               int(indices.numel()), int(exchange_slices), s.cuda_stream))
+                                               int(indices.numel()), int(exchange_slices), int(column_ranges), s.cuda_stream))
         info = self.info()
         self.rows_per_block, self.slices = info["rows_per_block"], info["exchange_slices"]
         self.local_rows, self.local_nnz, self.n_blocks = info["local_rows"], info["local_nnz"], info["n_blocks"]

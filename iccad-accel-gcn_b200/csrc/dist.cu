@@ -35,7 +35,6 @@ struct NcclApi {
     ncclResult_t (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int) = nullptr;
     ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
     ncclResult_t (*AllGather)(const void *, void *, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
-    ncclResult_t (*AllReduce)(const void *, void *, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
     const char *(*GetErrorString)(ncclResult_t) = nullptr;
 };
 
@@ -55,9 +54,8 @@ static int nccl_api(const NcclApi **out)
         api.CommInitRank = reinterpret_cast<decltype(api.CommInitRank)>(dlsym(h, "ncclCommInitRank"));
         api.CommDestroy = reinterpret_cast<decltype(api.CommDestroy)>(dlsym(h, "ncclCommDestroy"));
         api.AllGather = reinterpret_cast<decltype(api.AllGather)>(dlsym(h, "ncclAllGather"));
-        api.AllReduce = reinterpret_cast<decltype(api.AllReduce)>(dlsym(h, "ncclAllReduce"));
         api.GetErrorString = reinterpret_cast<decltype(api.GetErrorString)>(dlsym(h, "ncclGetErrorString"));
-        if (!api.GetUniqueId || !api.CommInitRank || !api.CommDestroy || !api.AllGather || !api.AllReduce || !api.GetErrorString) {
+        if (!api.GetUniqueId || !api.CommInitRank || !api.CommDestroy || !api.AllGather || !api.GetErrorString) {
             set_error("agcn_dist: libnccl.so.2 lacks a needed symbol");
             dlclose(h);
             return AGCN_ERR_CUDA;
@@ -79,12 +77,11 @@ static int nccl_api(const NcclApi **out)
 
 constexpr int DIST_SLOTS = 4;             // gathered operands that can be in flight at once
 constexpr int DIST_MAX_CHUNKS = 16;
-constexpr int DIST_COPY_STREAMS = 4;
 
 }  // namespace agcn
 
 struct agcn_dist {
-    int rank = 0, world = 1, chunks = 1;
+    int rank = 0, world = 1, chunks = 1, ranges = 1;     // exchange slices; column ranges of the block's tiled plan
     const agcn::NcclApi *nccl = nullptr;
     ncclComm_t comm = nullptr;
     cudaStream_t s_comm = nullptr;
@@ -93,8 +90,8 @@ struct agcn_dist {
     int64_t n = 0, per = 0, n_gathered = 0, local_rows = 0, local_nnz = 0, n_blocks = 0;
     int *indptr = nullptr, *idx = nullptr, *block4 = nullptr;
     float *val = nullptr;
-    agcn_spmm_plan *plan = nullptr;           // chunks == 1
-    agcn_spmm_tiled *tiled = nullptr;         // chunks > 1: one column range per exchanged slice
+    agcn_spmm_plan *plan = nullptr;           // ranges == 1
+    agcn_spmm_tiled *tiled = nullptr;         // ranges > 1: one column range per exchanged slice, or equal ranges of the gathered operand
     // gathered operands
     float *gathered[agcn::DIST_SLOTS] = {};
     size_t gathered_cap[agcn::DIST_SLOTS] = {};
@@ -105,18 +102,6 @@ struct agcn_dist {
     cudaEvent_t ev_input = nullptr;                                        // the caller's block is ready on its stream
     bool slot_used[agcn::DIST_SLOTS] = {};
     int launches_last_step = 0;
-    // push exchange (AGCN_DIST_EXCHANGE=push): every rank copies its block straight into every peer's
-    // gathered buffer with the copy engines; two buffers per slot, used alternately
-    int push = 0;
-    float *pbuf[agcn::DIST_SLOTS][2] = {};                              // this rank's buffers
-    float *pbuf_peer[agcn::DIST_SLOTS][2][agcn::DIST_MAX_WORLD] = {};   // the same buffers of every rank, mapped here
-    size_t pbuf_cap[agcn::DIST_SLOTS] = {};
-    int pbuf_next[agcn::DIST_SLOTS] = {};
-    cudaStream_t s_copy[agcn::DIST_COPY_STREAMS] = {};                   // the pushes run on several streams (several copy engines)
-    cudaEvent_t ev_copy[agcn::DIST_COPY_STREAMS] = {};
-    cudaEvent_t ev_fork = nullptr;
-    float *d_token = nullptr;                                           // one float: operand of the barrier all-reduce
-    unsigned char *d_handles = nullptr;                                 // [world][64]: exchange of IPC handles
 };
 
 struct agcn_gcn2 {
@@ -148,19 +133,6 @@ static void dist_free(agcn_dist *d)
         if (d->ev_consumed[s]) cudaEventDestroy(d->ev_consumed[s]);
     }
     if (d->ev_input) cudaEventDestroy(d->ev_input);
-    for (int s = 0; s < DIST_SLOTS; s++)
-        for (int b = 0; b < 2; b++) {
-            for (int r = 0; r < d->world; r++)
-                if (r != d->rank && d->pbuf_peer[s][b][r] != nullptr) cudaIpcCloseMemHandle(d->pbuf_peer[s][b][r]);
-            cudaFree(d->pbuf[s][b]);
-        }
-    for (int i = 0; i < DIST_COPY_STREAMS; i++) {
-        if (d->s_copy[i]) cudaStreamDestroy(d->s_copy[i]);
-        if (d->ev_copy[i]) cudaEventDestroy(d->ev_copy[i]);
-    }
-    if (d->ev_fork) cudaEventDestroy(d->ev_fork);
-    cudaFree(d->d_token);
-    cudaFree(d->d_handles);
     if (d->comm != nullptr && d->nccl != nullptr) d->nccl->CommDestroy(d->comm);
     if (d->s_comm) cudaStreamDestroy(d->s_comm);
     delete d;
@@ -188,16 +160,6 @@ static int dist_create(agcn_dist **out, int rank, int world, const void *id)
         static_assert(sizeof(uid) == AGCN_DIST_ID_BYTES, "AGCN_DIST_ID_BYTES must be sizeof(ncclUniqueId)");
         memcpy(&uid, id, sizeof(uid));
         AGCN_NCCL(d->nccl, d->nccl->CommInitRank(&d->comm, world, uid, rank));
-        const char *mode = getenv("AGCN_DIST_EXCHANGE");
-        d->push = mode != nullptr && strcmp(mode, "push") == 0 ? 1 : 0;
-        AGCN_CUDA(cudaMalloc(&d->d_token, sizeof(float)));
-        AGCN_CUDA(cudaMemset(d->d_token, 0, sizeof(float)));
-        AGCN_CUDA(cudaMalloc(&d->d_handles, (size_t)world * sizeof(cudaIpcMemHandle_t)));
-        for (int i = 0; i < DIST_COPY_STREAMS; i++) {
-            AGCN_CUDA(cudaStreamCreateWithFlags(&d->s_copy[i], cudaStreamNonBlocking));
-            AGCN_CUDA(cudaEventCreateWithFlags(&d->ev_copy[i], cudaEventDisableTiming));
-        }
-        AGCN_CUDA(cudaEventCreateWithFlags(&d->ev_fork, cudaEventDisableTiming));
     }
     guard.d = nullptr;
     *out = d;
@@ -206,13 +168,14 @@ static int dist_create(agcn_dist **out, int rank, int world, const void *id)
 
 // Builds this rank's block from the whole degree-ordered matrix on this device.
 static int dist_set_graph(agcn_dist *d, const int *d_indptr, const int *d_indices, const float *d_vals, int64_t n_rows,
-                          int64_t nnz, int chunks, cudaStream_t s)
+                          int64_t nnz, int chunks, int column_ranges, cudaStream_t s)
 {
     AGCN_REQUIRE(d != nullptr, "agcn_dist_set_graph: null context");
     AGCN_REQUIRE(d_indptr != nullptr && n_rows > 0 && n_rows < (int64_t)INT32_MAX / 2, "agcn_dist_set_graph: null indptr or bad n_rows");
     AGCN_REQUIRE(nnz >= 0 && nnz <= (int64_t)INT32_MAX && (nnz == 0 || (d_indices != nullptr && d_vals != nullptr)),
                  "agcn_dist_set_graph: bad nnz, or null indices / values");
     AGCN_REQUIRE(chunks >= 1 && chunks <= DIST_MAX_CHUNKS && chunks <= 32, "agcn_dist_set_graph: 1..%d exchange slices", DIST_MAX_CHUNKS);
+    AGCN_REQUIRE(column_ranges >= 1 && column_ranges <= 32, "agcn_dist_set_graph: 1..32 column ranges");
     dist_free_graph(d);
     for (int sl = 0; sl < DIST_SLOTS; sl++) d->slot_used[sl] = false;
 
@@ -270,7 +233,9 @@ static int dist_set_graph(agcn_dist *d, const int *d_indptr, const int *d_indice
         return AGCN_ERR_RANGE;
     }
 
-    if (chunks == 1) {
+    // sliced exchange: one column range per slice; otherwise the caller's choice of equal ranges
+    d->ranges = chunks > 1 ? chunks : column_ranges;
+    if (d->ranges == 1) {
         rc = partition_device(d->indptr, per, nullptr, 0, &d->n_blocks, s);
         if (rc != AGCN_OK) return rc;
         if (d->n_blocks > 0) {
@@ -280,110 +245,14 @@ static int dist_set_graph(agcn_dist *d, const int *d_indptr, const int *d_indice
         }
         return spmm_create(&d->plan, d->block4, d->n_blocks, d->idx, per, d->n_gathered, d->local_nnz, s);
     }
-    // one column range per exchanged slice: the product over a slice starts when that slice has arrived
-    std::vector<int> bounds((size_t)chunks + 1);
-    for (int c = 0; c <= chunks; c++) bounds[c] = (int)((int64_t)c * d->world * L.rows_per_chunk);
-    rc = agcn_spmm_tiled_create(&d->tiled, d->indptr, d->idx, d->val, per, d->n_gathered, d->local_nnz, bounds.data(), chunks, s);
+    // with a sliced exchange the product over a slice starts when that slice has arrived; with column
+    // ranges alone every launch gathers from one L2-sized slab of the gathered operand
+    std::vector<int> bounds((size_t)d->ranges + 1);
+    for (int c = 0; c <= d->ranges; c++)
+        bounds[c] = chunks > 1 ? (int)((int64_t)c * d->world * L.rows_per_chunk) : (int)(d->n_gathered * c / d->ranges);
+    rc = agcn_spmm_tiled_create(&d->tiled, d->indptr, d->idx, d->val, per, d->n_gathered, d->local_nnz, bounds.data(), d->ranges, s);
     if (rc != AGCN_OK) return rc;
     return agcn_spmm_tiled_info(d->tiled, nullptr, &d->n_blocks, nullptr, nullptr);
-}
-
-// All ranks have reached this point of their communication streams (a one-float all-reduce).
-static int dist_barrier(agcn_dist *d)
-{
-    AGCN_NCCL(d->nccl, d->nccl->AllReduce(d->d_token, d->d_token, 1, ncclFloat, ncclSum, d->comm, d->s_comm));
-    return AGCN_OK;
-}
-
-// (Re)allocates the two push buffers of a slot on every rank and maps every peer's buffers here.
-// Collective: every rank calls it for the same slot and size at the same point of its program.
-static int dist_push_buffers(agcn_dist *d, int slot, size_t need)
-{
-    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
-    // nobody may still be copying into, or reading from, the old buffers
-    int rc = dist_barrier(d);
-    if (rc != AGCN_OK) return rc;
-    AGCN_CUDA(cudaStreamSynchronize(d->s_comm));
-    AGCN_CUDA(cudaDeviceSynchronize());
-    for (int b = 0; b < 2; b++)
-        for (int r = 0; r < d->world; r++) {
-            if (r != d->rank && d->pbuf_peer[slot][b][r] != nullptr) AGCN_CUDA(cudaIpcCloseMemHandle(d->pbuf_peer[slot][b][r]));
-            d->pbuf_peer[slot][b][r] = nullptr;
-        }
-    rc = dist_barrier(d);                      // every mapping of the old buffers is closed before they are freed
-    if (rc != AGCN_OK) return rc;
-    AGCN_CUDA(cudaStreamSynchronize(d->s_comm));
-    for (int b = 0; b < 2; b++) {
-        if (d->pbuf[slot][b] != nullptr) AGCN_CUDA(cudaFree(d->pbuf[slot][b]));
-        d->pbuf[slot][b] = nullptr;
-    }
-    d->pbuf_cap[slot] = 0;
-    for (int b = 0; b < 2; b++) {
-        AGCN_CUDA(cudaMalloc(&d->pbuf[slot][b], need));
-        cudaIpcMemHandle_t mine;
-        AGCN_CUDA(cudaIpcGetMemHandle(&mine, d->pbuf[slot][b]));
-        AGCN_CUDA(cudaMemcpyAsync(d->d_handles + (size_t)d->rank * sizeof(mine), &mine, sizeof(mine), cudaMemcpyHostToDevice, d->s_comm));
-        AGCN_NCCL(d->nccl, d->nccl->AllGather(d->d_handles + (size_t)d->rank * sizeof(mine), d->d_handles, sizeof(mine), ncclChar,
-                                             d->comm, d->s_comm));
-        std::vector<cudaIpcMemHandle_t> all((size_t)d->world);
-        AGCN_CUDA(cudaMemcpyAsync(all.data(), d->d_handles, (size_t)d->world * sizeof(mine), cudaMemcpyDeviceToHost, d->s_comm));
-        AGCN_CUDA(cudaStreamSynchronize(d->s_comm));
-        for (int r = 0; r < d->world; r++) {
-            if (r == d->rank) { d->pbuf_peer[slot][b][r] = d->pbuf[slot][b]; continue; }
-            void *p = nullptr;
-            AGCN_CUDA(cudaIpcOpenMemHandle(&p, all[r], cudaIpcMemLazyEnablePeerAccess));
-            d->pbuf_peer[slot][b][r] = static_cast<float *>(p);
-        }
-    }
-    d->pbuf_cap[slot] = need;
-    d->pbuf_next[slot] = 0;
-    return AGCN_OK;
-}
-
-// The exchange by copy engines: this rank's block goes straight into every rank's gathered buffer
-// (peer copies over NVLink, no SM is used), then a one-float all-reduce tells every rank that all
-// copies into its buffer have completed.  The slot's two buffers alternate: a buffer is written
-// again two exchanges later, and the barrier of the exchange in between already proves that every
-// rank has finished the product that read it (a slot's product must be enqueued before the slot's
-// next exchange is begun).
-static int dist_push(agcn_dist *d, int slot, const float *d_x_block, int dim)
-{
-    const size_t need = (size_t)d->n_gathered * dim * sizeof(float);
-    if (need > d->pbuf_cap[slot]) {
-        int rc = dist_push_buffers(d, slot, need);
-        if (rc != AGCN_OK) return rc;
-    }
-    const int b = d->pbuf_next[slot];
-    d->pbuf_next[slot] ^= 1;
-    const int64_t slice_rows = d->layout.rows_per_chunk;
-    // each peer's copy is cut in two and the pieces are dealt over the copy streams, so that several
-    // copy engines work at once; the communication stream forks into them and joins before the barrier
-    const int64_t half_rows = (slice_rows + 1) / 2;
-    for (int c = 0; c < d->chunks; c++) {
-        const float *src = d_x_block + (int64_t)c * slice_rows * dim;
-        const int64_t dst_row = (int64_t)c * d->world * slice_rows + (int64_t)d->rank * slice_rows;
-        AGCN_CUDA(cudaEventRecord(d->ev_fork, d->s_comm));
-        for (int i = 0; i < DIST_COPY_STREAMS; i++) AGCN_CUDA(cudaStreamWaitEvent(d->s_copy[i], d->ev_fork, 0));
-        int piece = 0;
-        for (int i = 0; i < d->world; i++) {
-            const int r = (d->rank + i) % d->world;          // every rank starts with a different peer
-            for (int h = 0; h < 2; h++, piece++) {
-                const int64_t r0 = h * half_rows, r1 = h == 0 ? half_rows : slice_rows;
-                if (r1 <= r0) continue;
-                AGCN_CUDA(cudaMemcpyAsync(d->pbuf_peer[slot][b][r] + (dst_row + r0) * dim, src + r0 * dim,
-                                          (size_t)(r1 - r0) * dim * sizeof(float), cudaMemcpyDefault, d->s_copy[piece % DIST_COPY_STREAMS]));
-            }
-        }
-        for (int i = 0; i < DIST_COPY_STREAMS; i++) {
-            AGCN_CUDA(cudaEventRecord(d->ev_copy[i], d->s_copy[i]));
-            AGCN_CUDA(cudaStreamWaitEvent(d->s_comm, d->ev_copy[i], 0));
-        }
-        int rc = dist_barrier(d);
-        if (rc != AGCN_OK) return rc;
-        AGCN_CUDA(cudaEventRecord(d->ev_ready[slot][c], d->s_comm));
-    }
-    d->gathered_ptr[slot] = d->pbuf[slot][b];
-    return AGCN_OK;
 }
 
 static int dist_gather_begin(agcn_dist *d, int slot, const float *d_x_block, int dim, cudaStream_t s)
@@ -400,14 +269,6 @@ static int dist_gather_begin(agcn_dist *d, int slot, const float *d_x_block, int
     }
     AGCN_REQUIRE(d->comm != nullptr, "agcn_dist_gather_begin: the context was created without a communicator (id = NULL): "
                                      "exchange the operand yourself and call agcn_dist_spmm_on_gathered");
-    if (d->push) {
-        AGCN_CUDA(cudaEventRecord(d->ev_input, s));
-        AGCN_CUDA(cudaStreamWaitEvent(d->s_comm, d->ev_input, 0));
-        int rc = dist_push(d, slot, d_x_block, dim);
-        if (rc != AGCN_OK) return rc;
-        d->slot_used[slot] = true;
-        return AGCN_OK;
-    }
     const size_t need = (size_t)d->n_gathered * dim * sizeof(float);
     if (need > d->gathered_cap[slot]) {
         if (d->gathered[slot] != nullptr) AGCN_CUDA(cudaFree(d->gathered[slot]));
@@ -446,8 +307,8 @@ static int dist_spmm_gathered(agcn_dist *d, int slot, float *d_y_block, int dim,
         rc = spmm_run(d->plan, d->idx, d->val, x, dim, d_y_block, dim, dim, s, activation, 0);
         d->launches_last_step = d->plan->launches_last_run;
     } else {
-        for (int c = 0; c < d->chunks && rc == AGCN_OK; c++) {
-            AGCN_CUDA(cudaStreamWaitEvent(s, d->ev_ready[slot][c], 0));
+        for (int c = 0; c < d->ranges && rc == AGCN_OK; c++) {
+            if (c < d->chunks) AGCN_CUDA(cudaStreamWaitEvent(s, d->ev_ready[slot][c], 0));
             rc = agcn_spmm_tiled_run_range(d->tiled, c, x, dim, d_y_block, dim, dim, activation, s);
         }
         int launches = 0;
@@ -471,7 +332,7 @@ static int dist_spmm_on_gathered(agcn_dist *d, const float *d_gathered, float *d
         rc = spmm_run(d->plan, d->idx, d->val, d_gathered, dim, d_y_block, dim, dim, s, activation, 0);
         d->launches_last_step = d->plan->launches_last_run;
     } else {
-        for (int c = 0; c < d->chunks && rc == AGCN_OK; c++)
+        for (int c = 0; c < d->ranges && rc == AGCN_OK; c++)
             rc = agcn_spmm_tiled_run_range(d->tiled, c, d_gathered, dim, d_y_block, dim, dim, activation, s);
         int launches = 0;
         if (rc == AGCN_OK) rc = agcn_spmm_tiled_info(d->tiled, nullptr, nullptr, nullptr, &launches);
@@ -518,10 +379,11 @@ extern "C" int agcn_dist_destroy(agcn_dist *dist)
 }
 
 extern "C" int agcn_dist_set_graph(agcn_dist *dist, const int32_t *d_indptr, const int32_t *d_indices, const float *d_vals,
-                                   int64_t n_rows, int64_t nnz, int exchange_slices, void *stream)
+                                   int64_t n_rows, int64_t nnz, int exchange_slices, int column_ranges, void *stream)
 {
     agcn::clear_error();
-    int rc = agcn::dist_set_graph(dist, d_indptr, d_indices, d_vals, n_rows, nnz, exchange_slices, static_cast<cudaStream_t>(stream));
+    int rc = agcn::dist_set_graph(dist, d_indptr, d_indices, d_vals, n_rows, nnz, exchange_slices, column_ranges,
+                                  static_cast<cudaStream_t>(stream));
     if (rc != AGCN_OK && dist != nullptr) agcn::dist_free_graph(dist);
     return rc;
 }

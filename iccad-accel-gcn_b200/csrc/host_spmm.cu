@@ -5,9 +5,9 @@
 // What crosses PCIe is fixed by the call (the graph, X per product up; Y per product down), so
 // the work is to keep both copy engines and the SMs busy at once:
 //  - uploads, kernels and downloads run on three streams chained by events;
-//  - a product is launched as several unit ranges (a unit = 8 consecutive tuples), and the rows a
-//    range completes are downloaded while the next range computes; rows that the carry kernel
-//    finishes (heavy rows crossing unit boundaries) come down after it;
+//  - a product is launched as several unit ranges (a unit = 8 consecutive tuples); each range is
+//    followed by the carry kernel over the carry slots of the rows it completes, and those rows are
+//    downloaded while the next range computes;
 //  - when the graph itself is part of the call (agcn_spmm_host_batch), column ids and values are
 //    uploaded in the same ranges and every range is multiplied -- for all products -- as soon as
 //    it has arrived, so the kernels and the downloads hide under the upload of A.
@@ -36,7 +36,9 @@ struct agcn_host_ctx {
     int64_t n_rows = 0, n_cols = 0, nnz = 0, n_blocks = 0;
     // unit ranges a product is issued in, with the first row / first nonzero of each boundary
     std::vector<int64_t> part_unit, part_row, part_loc;
-    int64_t first_deferred_row = 0;                   // rows from here on are complete only after the carry kernel
+    std::vector<int64_t> part_slot;                   // carry slots [part_slot[k], part_slot[k+1]) finish the rows of range k
+    std::vector<int2> h_unit_carry;                   // host copies of the plan's carry bookkeeping
+    std::vector<int> h_carry_row;
     int *d_abort = nullptr;                           // device word: set when a column id is out of range
     std::vector<cudaEvent_t> events;
     size_t events_used = 0;
@@ -117,6 +119,29 @@ static void plan_parts(agcn_host_ctx *c, const int *h_block4, int want_parts)
     c->part_unit.push_back(n_units);
     c->part_row.push_back(c->n_rows);
     c->part_loc.push_back(c->nnz);
+    // Carry slots are handed out in unit order (a slot for the row entering a unit from the left,
+    // one for the row leaving it to the right).  The rows a unit range completes own the slots up
+    // to the first slot of the row that runs on into the next range, or -- if none does -- up to the
+    // first slot of the next range's first unit.
+    const int n_parts = (int)c->part_unit.size() - 1;
+    const int64_t n_carry = (int64_t)c->h_carry_row.size();
+    c->part_slot.assign(n_parts + 1, n_carry);
+    c->part_slot[0] = 0;
+    int64_t next_slot = 0;                // slots handed out to the units before u
+    int k = 1;
+    for (int64_t u = 0; u < n_units && k < n_parts; u++) {
+        const int2 uc = c->h_unit_carry[u];
+        if (u == c->part_unit[k]) {
+            int64_t first = next_slot;
+            if (uc.x >= 0) {              // a row enters this unit from the previous range: back to its first slot
+                first = uc.x;
+                while (first > 0 && c->h_carry_row[first - 1] == c->h_carry_row[uc.x]) first--;
+            }
+            c->part_slot[k++] = first;
+        }
+        if (uc.x >= 0 && uc.x >= next_slot) next_slot = uc.x + 1;
+        if (uc.y >= 0 && uc.y >= next_slot) next_slot = uc.y + 1;
+    }
 }
 
 static int check_graph_args(agcn_host_ctx *ctx, const int *h_block4, int64_t n_blocks, const int *h_indices,
@@ -130,10 +155,8 @@ static int check_graph_args(agcn_host_ctx *ctx, const int *h_block4, int64_t n_b
     return AGCN_OK;
 }
 
-// Uploads .block4 and builds the plan.  Column ids are validated by the caller of this function
-// (whole array, or range by range as they arrive).
-static int upload_block4_and_plan(agcn_host_ctx *c, const int *h_block4, int64_t n_blocks, int64_t n_rows, int64_t n_cols,
-                                  int64_t nnz)
+// Starts the upload of .block4 (the first thing the plan needs) on the upload stream.
+static int upload_block4(agcn_host_ctx *c, const int *h_block4, int64_t n_blocks, int64_t n_rows, int64_t n_cols, int64_t nnz)
 {
     plan_free(c->plan);
     c->plan = nullptr;
@@ -146,17 +169,24 @@ static int upload_block4_and_plan(agcn_host_ctx *c, const int *h_block4, int64_t
     if (c->d_abort == nullptr) AGCN_CUDA(cudaMalloc(&c->d_abort, sizeof(int)));
     AGCN_CUDA(cudaMemsetAsync(c->d_abort, 0, sizeof(int), c->s_run));
     if (n_blocks > 0) AGCN_CUDA(cudaMemcpyAsync(c->graph[0], h_block4, bytes[0], cudaMemcpyHostToDevice, c->s_up));
-    int rc = ctx_chain(c, c->s_up, c->s_run);
+    return ctx_chain(c, c->s_up, c->s_run);
+}
+
+// Builds the plan from the uploaded .block4 (tuple validation, carry slots, uncovered rows;
+// synchronises s_run) and fetches its carry bookkeeping for plan_parts.  Column ids are validated
+// by the caller (whole array, or range by range as they arrive).
+static int build_plan(agcn_host_ctx *c)
+{
+    int rc = spmm_create(&c->plan, static_cast<const int *>(c->graph[0]), c->n_blocks, nullptr, c->n_rows, c->n_cols, c->nnz, c->s_run);
     if (rc != AGCN_OK) return rc;
-    // tuple validation, carry slots, uncovered rows (synchronises s_run)
-    rc = spmm_create(&c->plan, static_cast<const int *>(c->graph[0]), n_blocks, nullptr, n_rows, n_cols, nnz, c->s_run);
-    if (rc != AGCN_OK) return rc;
-    c->first_deferred_row = n_rows;
+    c->h_unit_carry.assign((size_t)c->plan->n_units, make_int2(-1, -1));
+    c->h_carry_row.assign((size_t)c->plan->n_carry, 0);
     if (c->plan->n_carry > 0) {
-        int first = 0;       // carry slots are assigned in unit order, so their rows ascend
-        AGCN_CUDA(cudaMemcpyAsync(&first, c->plan->carry_row, sizeof(int), cudaMemcpyDeviceToHost, c->s_run));
+        AGCN_CUDA(cudaMemcpyAsync(c->h_unit_carry.data(), c->plan->unit_carry, c->h_unit_carry.size() * sizeof(int2),
+                                  cudaMemcpyDeviceToHost, c->s_run));
+        AGCN_CUDA(cudaMemcpyAsync(c->h_carry_row.data(), c->plan->carry_row, c->h_carry_row.size() * sizeof(int),
+                                  cudaMemcpyDeviceToHost, c->s_run));
         AGCN_CUDA(cudaStreamSynchronize(c->s_run));
-        c->first_deferred_row = first;
     }
     return AGCN_OK;
 }
@@ -171,10 +201,12 @@ static int host_set_graph(agcn_host_ctx *c, const int *h_block4, int64_t n_block
     if (rc == AGCN_OK) rc = reserve(&c->graph[2], &c->graph_cap[2], nnz > 0 ? (size_t)nnz * 4 : 16);
     if (rc == AGCN_OK) rc = reserve(&c->graph[0], &c->graph_cap[0], n_blocks > 0 ? (size_t)n_blocks * 16 : 16);
     if (rc != AGCN_OK) return rc;
-    rc = upload_block4_and_plan(c, h_block4, n_blocks, n_rows, n_cols, nnz);
+    rc = upload_block4(c, h_block4, n_blocks, n_rows, n_cols, nnz);
     if (rc != AGCN_OK) return rc;
+    if (nnz > 0) AGCN_CUDA(cudaMemcpyAsync(c->graph[1], h_indices, (size_t)nnz * 4, cudaMemcpyHostToDevice, c->s_up));
+    rc = build_plan(c);                   // on the host and s_run, while the column ids go up
+    if (rc != AGCN_OK) { ctx_sync(c); return rc; }
     if (nnz > 0) {
-        AGCN_CUDA(cudaMemcpyAsync(c->graph[1], h_indices, (size_t)nnz * 4, cudaMemcpyHostToDevice, c->s_up));
         rc = ctx_chain(c, c->s_up, c->s_run);
         if (rc != AGCN_OK) return rc;
         rc = spmm_check_cols(static_cast<const int *>(c->graph[1]), nnz, n_cols, c->d_abort, c->s_run);   // under the upload of the values
@@ -256,20 +288,16 @@ static int host_products(agcn_host_ctx *c, int n, const float *const *h_x, float
             continue;
         }
         for (int k = 0; k < n_parts; k++) {
+            // the units of the range, then the carry kernel over the rows the range completes
             SpmmLaunchPart part;
             part.unit0 = c->part_unit[k]; part.unit1 = c->part_unit[k + 1];
-            part.zero_fill = k == 0; part.carry = false;
+            part.zero_fill = k == 0;
+            part.carry_s0 = c->part_slot[k]; part.carry_s1 = c->part_slot[k + 1];
             rc = spmm_run_prepared(c->plan, idx, val, static_cast<const float *>(c->xbuf[i]), dim, true, y, dim, dim, c->s_run, 0, 0, part);
             if (rc == AGCN_OK) rc = ctx_chain(c, c->s_run, c->s_down);
-            if (rc == AGCN_OK) rc = download_rows(c, i, h_y[i], dim, c->part_row[k], std::min(c->part_row[k + 1], c->first_deferred_row));
+            if (rc == AGCN_OK) rc = download_rows(c, i, h_y[i], dim, c->part_row[k], c->part_row[k + 1]);
             if (rc != AGCN_OK) { ctx_sync(c); return rc; }
         }
-        SpmmLaunchPart tail;                  // no units: only the carry kernel
-        tail.unit0 = tail.unit1 = c->plan->n_units; tail.zero_fill = false; tail.carry = true;
-        rc = spmm_run_prepared(c->plan, idx, val, static_cast<const float *>(c->xbuf[i]), dim, true, y, dim, dim, c->s_run, 0, 0, tail);
-        if (rc == AGCN_OK) rc = ctx_chain(c, c->s_run, c->s_down);
-        if (rc == AGCN_OK) rc = download_rows(c, i, h_y[i], dim, c->first_deferred_row, c->n_rows);
-        if (rc != AGCN_OK) { ctx_sync(c); return rc; }
     }
     return ctx_sync(c);
 }
@@ -295,10 +323,15 @@ static int host_graph_and_products(agcn_host_ctx *c, const int *h_block4, int64_
     const auto host_t0 = std::chrono::steady_clock::now();
     c->timed = false;
     AGCN_CUDA(cudaEventRecord(c->t_up0, c->s_up));
-    rc = upload_block4_and_plan(c, h_block4, n_blocks, n_rows, n_cols, nnz);
-    if (rc != AGCN_OK) return rc;
-    rc = reserve_products(c, n, dims, true);
-    if (rc != AGCN_OK) return rc;
+    // .block4 first, then every X behind it: the plan is built (on the host and on s_run) under those uploads
+    rc = upload_block4(c, h_block4, n_blocks, n_rows, n_cols, nnz);
+    if (rc == AGCN_OK) rc = reserve_products(c, n, dims, false);
+    if (rc != AGCN_OK) { ctx_sync(c); return rc; }
+    for (int i = 0; i < n; i++)
+        AGCN_CUDA(cudaMemcpyAsync(c->xbuf[i], h_x[i], (size_t)n_cols * dims[i] * 4, cudaMemcpyHostToDevice, c->s_up));
+    rc = build_plan(c);
+    if (rc == AGCN_OK) rc = reserve_products(c, n, dims, true);       // now that the number of carry slots is known
+    if (rc != AGCN_OK) { ctx_sync(c); return rc; }
     const auto host_t1 = std::chrono::steady_clock::now();
     // ranges of about 32 MB of (column id, value) pairs: long enough for full PCIe speed, short
     // enough that the first product starts early and the last download is short
@@ -306,8 +339,6 @@ static int host_graph_and_products(agcn_host_ctx *c, const int *h_block4, int64_
     const int n_parts = (int)c->part_unit.size() - 1;
     int *idx = static_cast<int *>(c->graph[1]);
     float *val = static_cast<float *>(c->graph[2]);
-    for (int i = 0; i < n; i++)
-        AGCN_CUDA(cudaMemcpyAsync(c->xbuf[i], h_x[i], (size_t)n_cols * dims[i] * 4, cudaMemcpyHostToDevice, c->s_up));
     for (int k = 0; k < n_parts; k++) {
         const int64_t p0 = c->part_loc[k], p1 = c->part_loc[k + 1];
         AGCN_CUDA(cudaMemcpyAsync(idx + p0, h_indices + p0, (size_t)(p1 - p0) * 4, cudaMemcpyHostToDevice, c->s_up));
@@ -320,27 +351,18 @@ static int host_graph_and_products(agcn_host_ctx *c, const int *h_block4, int64_
         for (int i = 0; i < n && rc == AGCN_OK; i++) {
             SpmmLaunchPart part;
             part.unit0 = c->part_unit[k]; part.unit1 = c->part_unit[k + 1];
-            part.zero_fill = k == 0; part.carry = false; part.abort_flag = c->d_abort;
+            part.zero_fill = k == 0; part.abort_flag = c->d_abort;
+            part.carry_s0 = c->part_slot[k]; part.carry_s1 = c->part_slot[k + 1];
             part.carry_buf = static_cast<float *>(c->cbuf[i]);
             rc = spmm_run_prepared(c->plan, idx, val, static_cast<const float *>(c->xbuf[i]), dims[i], true,
                                    static_cast<float *>(c->ybuf[i]), dims[i], dims[i], c->s_run, 0, 0, part);
         }
         if (rc == AGCN_OK) rc = ctx_chain(c, c->s_run, c->s_down);
         for (int i = 0; i < n && rc == AGCN_OK; i++)
-            rc = download_rows(c, i, h_y[i], dims[i], c->part_row[k], std::min(c->part_row[k + 1], c->first_deferred_row));
-        if (rc != AGCN_OK) { ctx_sync(c); return rc; }
-    }
-    for (int i = 0; i < n; i++) {
-        SpmmLaunchPart tail;
-        tail.unit0 = tail.unit1 = c->plan->n_units; tail.zero_fill = false; tail.carry = true; tail.abort_flag = c->d_abort;
-        tail.carry_buf = static_cast<float *>(c->cbuf[i]);
-        rc = spmm_run_prepared(c->plan, idx, val, static_cast<const float *>(c->xbuf[i]), dims[i], true,
-                               static_cast<float *>(c->ybuf[i]), dims[i], dims[i], c->s_run, 0, 0, tail);
+            rc = download_rows(c, i, h_y[i], dims[i], c->part_row[k], c->part_row[k + 1]);
         if (rc != AGCN_OK) { ctx_sync(c); return rc; }
     }
     AGCN_CUDA(cudaEventRecord(c->t_run1, c->s_run));
-    rc = ctx_chain(c, c->s_run, c->s_down);
-    for (int i = 0; i < n && rc == AGCN_OK; i++) rc = download_rows(c, i, h_y[i], dims[i], c->first_deferred_row, n_rows);
     AGCN_CUDA(cudaEventRecord(c->t_down1, c->s_down));
     c->host_plan_ms = std::chrono::duration<float, std::milli>(host_t1 - host_t0).count();
     c->host_enqueue_ms = std::chrono::duration<float, std::milli>(std::chrono::steady_clock::now() - host_t0).count();

@@ -43,6 +43,7 @@ int spmm_prepare_x(agcn_spmm_plan *p, const float *d_x, int64_t ldx, int dim, cu
 struct SpmmLaunchPart {
     int64_t unit0 = 0, unit1 = -1;      // units [unit0, unit1); -1 = to the end
     bool zero_fill = true, carry = true;
+    int64_t carry_s0 = 0, carry_s1 = -1; // carry slots the carry kernel covers (-1 = to the last); row-aligned
     const int *abort_flag = nullptr;    // optional device word: nonzero makes the kernels return at once
     float *carry_buf = nullptr;         // optional carry scratch [n_carry][128] to use instead of the plan's (products in flight together)
 };

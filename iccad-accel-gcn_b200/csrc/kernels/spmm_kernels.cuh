@@ -357,18 +357,20 @@ spmm_units_kernel(const SpmmParams p)
 
 // Adds the carried partials of every row that crosses unit boundaries, in
 // unit order, and stores the row.  One warp per carry slot; the warp of the
-// first slot of a row does the work.
+// first slot of a row does the work.  The launch covers slots [s0, s1), a range
+// that begins and ends between rows (all slots by default; a product issued in
+// unit ranges finishes the rows of each range as soon as its units have run).
 template <bool VEC>
 __global__ void __launch_bounds__(SPMM_THREADS)
-spmm_carry_kernel(const float *__restrict__ carry, const int *__restrict__ carry_row, int64_t n_carry,
+spmm_carry_kernel(const float *__restrict__ carry, const int *__restrict__ carry_row, int64_t s0, int64_t s1,
                   float *y, int64_t ldy, int dim, int relu, int accumulate, int y_vec, int dim_store)
 {
-    const int64_t s = (int64_t)blockIdx.x * SPMM_WARPS + warp_id();
-    if (s >= n_carry) return;
+    const int64_t s = s0 + (int64_t)blockIdx.x * SPMM_WARPS + warp_id();
+    if (s >= s1) return;
     const int row = carry_row[s];
-    if (s > 0 && carry_row[s - 1] == row) return;
+    if (s > s0 && carry_row[s - 1] == row) return;
     int64_t s_end = s + 1;
-    while (s_end < n_carry && carry_row[s_end] == row) s_end++;
+    while (s_end < s1 && carry_row[s_end] == row) s_end++;
     const int lane = lane_id();
     if (VEC) {
         const int col = lane * 4;

@@ -233,7 +233,9 @@ int spmm_run_prepared(agcn_spmm_plan *p, const int *d_indices, const float *d_va
         if (x_bytes > 0.75 * (double)p->l2_bytes && x_bytes <= 4.0 * (double)p->l2_bytes) panel = 64;
     }
     if (p->panel_override > 0) panel = p->panel_override;
-    const bool whole = unit0 == 0 && unit1 == p->n_units && part.carry;
+    const int64_t cs0 = part.carry_s0, cs1 = part.carry_s1 < 0 ? p->n_carry : part.carry_s1;
+    AGCN_REQUIRE(cs0 >= 0 && cs0 <= cs1 && cs1 <= p->n_carry, "agcn_spmm_run: carry slot range outside the plan");
+    const bool whole = unit0 == 0 && unit1 == p->n_units && part.carry && cs0 == 0 && cs1 == p->n_carry;
     // A carry slot holds SPMM_PANEL floats and every column pass uses its own columns of it, so a
     // product of up to SPMM_PANEL columns can be issued in parts (unit launches now, carry kernel
     // later) whatever its passes are -- with the same passes, hence the same bits, as a whole run.
@@ -265,10 +267,10 @@ int spmm_run_prepared(agcn_spmm_plan *p, const int *d_indices, const float *d_va
             AGCN_LAUNCH_CHECK("spmm_units_kernel");
             p->launches_last_run++;
         }
-        if (p->n_carry > 0 && part.carry) {
-            const unsigned cgrid = (unsigned)ceil_div(p->n_carry, SPMM_WARPS);
+        if (cs1 > cs0 && part.carry) {
+            const unsigned cgrid = (unsigned)ceil_div(cs1 - cs0, SPMM_WARPS);
             auto k = vec ? spmm_carry_kernel<true> : spmm_carry_kernel<false>;
-            AGCN_KERNEL(k, cgrid, SPMM_THREADS, s, (const float *)prm.carry, (const int *)p->carry_row, p->n_carry, prm.y, ldy,
+            AGCN_KERNEL(k, cgrid, SPMM_THREADS, s, (const float *)prm.carry, (const int *)p->carry_row, cs0, cs1, prm.y, ldy,
                         prm.dim, activation, accumulate, prm.y_vec, prm.dim_store);
             AGCN_LAUNCH_CHECK("spmm_carry_kernel");
             p->launches_last_run++;

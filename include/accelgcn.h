@@ -306,7 +306,11 @@ int agcn_host_last_timing(agcn_host_ctx *ctx, float *ms6);
  * builds .block4 metadata and the plan for the block.  exchange_slices > 1
  * exchanges the operand in that many row slices and cuts the block's columns
  * the same way (agcn_spmm_tiled), so the product over a slice starts as soon
- * as the slice has arrived instead of after the whole all-gather.
+ * as the slice has arrived instead of after the whole all-gather.  With one
+ * slice, column_ranges > 1 cuts the block's columns into that many equal
+ * ranges of the gathered operand (for a gathered operand larger than L2:
+ * agcn_spmm_tiled_suggest(rows_per_block, world * rows_per_block, local nnz,
+ * dim) says how many); 1 = no tiling.
  *
  * Dense operands are "block rows": [rows_per_block x dim] per rank, row j =
  * local row j, padding rows zero.  agcn_dist_block_rows writes, for any rank,
@@ -322,13 +326,6 @@ int agcn_host_last_timing(agcn_host_ctx *ctx, float *ms6);
  * is read in place (it must stay valid until the product has run).  All calls
  * are asynchronous; every rank must issue the same sequence of exchanges, and a
  * slot's product must be enqueued before the slot's next exchange is begun.
- *
- * The exchange itself is ncclAllGather by default.  With the environment
- * variable AGCN_DIST_EXCHANGE=push (read by agcn_dist_create) every rank instead
- * copies its block straight into every peer's gathered buffer with the copy
- * engines (CUDA IPC mappings of buffers the library allocates, peer copies over
- * NVLink, no SM is taken from the products running beside it) and a one-float
- * all-reduce marks the arrival; all ranks must then be processes on one node.
  * ---------------------------------------------------------------------- */
 #define AGCN_MAX_WORLD      64
 #define AGCN_DIST_ID_BYTES 128
@@ -347,7 +344,7 @@ int agcn_dist_create(agcn_dist **dist, int rank, int world, const void *id);
 int agcn_dist_destroy(agcn_dist *dist);
 int agcn_dist_set_graph(agcn_dist *dist, const int32_t *d_indptr, const int32_t *d_indices,
                         const float *d_vals, int64_t n_rows, int64_t nnz, int exchange_slices,
-                        void *stream);
+                        int column_ranges, void *stream);
 int agcn_dist_info(const agcn_dist *dist, int64_t *rows_per_block, int64_t *local_rows,
                    int64_t *local_nnz, int64_t *n_blocks, int *exchange_slices,
                    int *launches_last_step);

@@ -234,8 +234,8 @@ def test_parity_with_the_reference_kernel_heavy_rows(cfg4_small):
     assert spmm_close(y, cs, row_abs_scale(cfg4_small.indptr, cfg4_small.val, x)).all()
 
 
-@pytest.mark.parametrize("world,slices", [(2, 1), (5, 1), (4, 3), (8, 2)])
-def test_row_sharded_product_on_one_gpu_equals_unsharded(cfg4_small, world, slices):
+@pytest.mark.parametrize("world,slices,ranges", [(2, 1, 1), (5, 1, 1), (4, 3, 1), (8, 2, 1), (4, 1, 3), (1, 1, 2)])
+def test_row_sharded_product_on_one_gpu_equals_unsharded(cfg4_small, world, slices, ranges):
     # every rank's block built and multiplied in this one process (contexts without a communicator:
     # the all-gather is replaced by assembling the gathered operand by hand): two row ranges per
     # rank, column ids renamed to gathered positions, block-local .block4
@@ -246,7 +246,9 @@ def test_row_sharded_product_on_one_gpu_equals_unsharded(cfg4_small, world, slic
     ip, ix, v = (torch.from_numpy(a).to(dev) for a in (c.indptr, c.idx, c.val))
     x = c.x(64)
     xt = torch.from_numpy(x).to(dev)
-    shards = [sharded.ShardedSpmm(ip, ix, v, r, world, exchange_slices=slices, communicator=False) for r in range(world)]
+    # (ranges > 1: the block's columns tiled into equal ranges of the gathered operand, one exchange)
+    shards = [sharded.ShardedSpmm(ip, ix, v, r, world, exchange_slices=slices, communicator=False, column_ranges=ranges)
+              for r in range(world)]
     gathered = shards[0].assemble_gathered([sh.to_block(xt) for sh in shards])
     blocks = []
     for sh in shards:
