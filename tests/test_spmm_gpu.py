@@ -556,6 +556,9 @@ def test_host_batch_and_streamed_graph(cfg1, cfg4_small):
         ys = h.step_batch(c.block4, c.idx, c.val, xs[:4], c.n)              # streamed (all widths multiples of 4)
         for x, y in zip(xs[:4], ys):
             c.check(x, y)
+        t = h.last_timing()                                                  # where the time of that call went
+        assert 0 <= t["first_kernel_started"] <= t["last_kernel_finished"] <= t["last_y_downloaded"] + 1e-3
+        assert t["a_uploaded"] > 0 and t["host_all_enqueued"] >= t["host_plan_built"] > 0
         ys_all = h.step_batch(c.block4, c.idx, c.val, xs, c.n)              # 33 columns: upload first, then multiply
         for x, y in zip(xs, ys_all):
             c.check(x, y)
