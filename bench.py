@@ -323,20 +323,22 @@ def pcie_peaks(dev, mb=512):
     return out
 
 
-def checksum_check(ip, ix, v, n, xs_full, ys, shard, dims, dev, world):
-    """1^T (A X) = (1^T A) X in fp64 over all ranks' rows, and a row sample of this rank's block against
-    the fp64 product from the whole matrix (every rank still holds it at this point)."""
+def checksum_check(ip, ix, v, n, xs_full, ys, shard_of, col_of, dims, dev, world):
+    """1^T (A X) = (1^T A) X in fp64 over all ranks' rows (and column groups), and a row sample of this
+    rank's block against the fp64 product from the whole matrix (every rank still holds it at this point)."""
     import torch
     import torch.distributed as dist
     col_weight = torch.zeros(n, dtype=torch.float64, device=dev).index_add_(0, ix.to(torch.int64), v.to(torch.float64))
-    rows = shard.rows_of()
-    valid = torch.nonzero(rows >= 0).reshape(-1)
-    pick = valid[torch.randint(0, valid.numel(), (64,), device=dev)]
-    pick = torch.unique(torch.cat([pick, valid[:1], valid[-1:]]))
     ok = True
     worst = 0.0
     for d in dims:
-        got = ys[d].to(torch.float64).sum(0)
+        rows = shard_of[d].rows_of()
+        c0, c1 = col_of[d]
+        valid = torch.nonzero(rows >= 0).reshape(-1)
+        pick = valid[torch.randint(0, valid.numel(), (64,), device=dev)]
+        pick = torch.unique(torch.cat([pick, valid[:1], valid[-1:]]))
+        got = torch.zeros(d, dtype=torch.float64, device=dev)
+        got[c0:c1] = ys[d].to(torch.float64).sum(0)
         if world > 1:
             dist.all_reduce(got)
         want = col_weight @ xs_full[d].to(torch.float64)
@@ -344,7 +346,7 @@ def checksum_check(ip, ix, v, n, xs_full, ys, shard, dims, dev, world):
         for j in pick.tolist():
             r = int(rows[j])
             a, b = int(ip[r]), int(ip[r + 1])
-            ref = (v[a:b].to(torch.float64)[:, None] * xs_full[d][ix[a:b].to(torch.int64)].to(torch.float64)).sum(0)
+            ref = (v[a:b].to(torch.float64)[:, None] * xs_full[d][ix[a:b].to(torch.int64), c0:c1].to(torch.float64)).sum(0)
             scale = max(1.0, float(v[a:b].abs().sum()))
             err = float(((ys[d][j].to(torch.float64) - ref).abs() - 1e-4 * ref.abs()).max())
             worst = max(worst, err / scale)
@@ -384,8 +386,19 @@ def ours(args, rank, world, local_rank):
     # (--slices S: widths of at least --slices-min-dim columns exchange their operand in S row slices and
     # multiply slice by slice, on a second context of the same layout; narrower widths keep one slice)
     sliced = world > 1 and args.slices > 1
+    # rows x features (--feature-groups F): a width of at least F * --feature-groups-min-width columns is
+    # multiplied as F independent row-sharded products of dim / F columns, each over world / F ranks with its
+    # own communicator -- 1 / F of the exchange among 1 / F of the ranks, blocks of F times the rows
+    fg = 1
+    if world > 1:
+        fg = args.feature_groups if args.feature_groups > 0 else (2 if world >= 8 else 1)
+        assert world % fg == 0, "--feature-groups must divide the number of GPUs"
+    fg_dims = [d for d in dims if fg > 1 and not sliced and d % fg == 0 and d // fg >= args.feature_groups_min_width]
     shard = sharded.ShardedSpmm(ip, ix, v, rank, world)
     shard_of = {d: shard for d in dims}
+    col_of = {d: (0, d) for d in dims}
+    ranges_of = {d: 1 for d in dims}
+    lib = _lib.load()
     if sliced and any(d >= args.slices_min_dim for d in dims):
         shard_sliced = sharded.ShardedSpmm(ip, ix, v, rank, world, exchange_slices=args.slices)
         assert shard_sliced.rows_per_block == shard.rows_per_block, "--slices must divide the block height"
@@ -393,15 +406,31 @@ def ours(args, rank, world, local_rank):
     elif world > 1 and args.tiled != "off":
         # a gathered operand that does not fit L2 is multiplied column range by column range (as on one GPU):
         # widths that want the same number of ranges share one more context of the same layout
-        lib = _lib.load()
         by_ranges = {}
         for d in dims:
             k = lib.agcn_spmm_tiled_suggest(shard.rows_per_block, shard.n_gathered, shard.local_nnz, d)
-            if k > 1:
+            if k > 1 and d not in fg_dims:
                 by_ranges.setdefault(k, []).append(d)
         for k, ds in by_ranges.items():
             tiled_shard = sharded.ShardedSpmm(ip, ix, v, rank, world, column_ranges=k)
             shard_of.update({d: tiled_shard for d in ds})
+            ranges_of.update({d: "tiled" for d in ds})
+    if fg_dims:
+        row_rank, row_world, fgroup, _members = sharded.feature_groups(rank, world, fg)
+        groups = [dist.new_group(ranks=list(range(j, world, fg))) for j in range(fg)]      # every rank makes every group
+        grp = groups[fgroup] if row_world > 1 else None
+        fg_shard = sharded.ShardedSpmm(ip, ix, v, row_rank, row_world, group=grp)
+        fg_tiled = {}
+        for d in fg_dims:
+            w = d // fg
+            col_of[d] = (fgroup * w, (fgroup + 1) * w)
+            k = 1
+            if args.tiled != "off":
+                k = lib.agcn_spmm_tiled_suggest(fg_shard.rows_per_block, fg_shard.n_gathered, fg_shard.local_nnz, w)
+            if k > 1 and k not in fg_tiled:
+                fg_tiled[k] = sharded.ShardedSpmm(ip, ix, v, row_rank, row_world, group=grp, column_ranges=k)
+            shard_of[d] = fg_tiled[k] if k > 1 else fg_shard
+            ranges_of[d] = "tiled" if k > 1 else 1
     per = shard.rows_per_block
     n_blocks_local = int(shard.n_blocks)
     nb = torch.tensor([n_blocks_local], dtype=torch.int64, device=dev)
@@ -409,8 +438,9 @@ def ours(args, rank, world, local_rank):
         dist.all_reduce(nb)
     n_blocks = int(nb.item())
     xs_full = {d: synth.features(n, d, g.info["seed"], dev) for d in dims}
-    xs = {d: shard.to_block(xs_full[d]) for d in dims}
-    ys = {d: torch.empty((per, d), dtype=torch.float32, device=dev) for d in dims}
+    xs = {d: shard_of[d].to_block(xs_full[d] if col_of[d] == (0, d) else xs_full[d][:, col_of[d][0]:col_of[d][1]].contiguous())
+          for d in dims}
+    ys = {d: torch.empty_like(xs[d]) for d in dims}
     # single GPU: a product whose X does not stay in L2 runs column-tiled (A regrouped by column range)
     tiled = {}
     if world == 1 and args.tiled != "off":
@@ -460,7 +490,7 @@ def ours(args, rank, world, local_rank):
     launches_per_step = count_launches()
     barrier()
     # the step's results against the fp64 product, once, before anything is timed
-    verified = checksum_check(ip, ix, v, n, xs_full, ys, shard, dims, dev, world)
+    verified = checksum_check(ip, ix, v, n, xs_full, ys, shard_of, col_of, dims, dev, world)
     del xs_full
     if world > 1:
         del ip, ix, v
@@ -529,9 +559,12 @@ def ours(args, rank, world, local_rank):
                  "exchanges_without_products_ms": exchange_ms, "exchange": "ncclAllGather inside the library",
                  "step_minus_products_ms": total_ms / args.steps - compute_ms,
                  "exchange_slices": {str(d): shard_of[d].slices for d in dims},
-                 "column_ranges": {str(d): (1 if shard_of[d] is shard else "tiled") for d in dims},
-                 "rows_per_block": per, "max_local_nnz_over_mean": float(nnz_max.item()) * world / nnz,
-                 "exchanged_bytes_in_per_rank_per_step": 4 * sum(dims) * per * (world - 1),
+                 "column_ranges": {str(d): ranges_of[d] for d in dims},
+                 "feature_groups": {str(d): (fg if d in fg_dims else 1) for d in dims},
+                 "rows_per_block": {str(d): shard_of[d].rows_per_block for d in dims},
+                 "max_local_nnz_over_mean": float(nnz_max.item()) * world / nnz,
+                 "exchanged_bytes_in_per_rank_per_step": sum(4 * (col_of[d][1] - col_of[d][0]) * shard_of[d].rows_per_block
+                                                             * (shard_of[d].world - 1) for d in dims),
                  "limiting_phase": "products" if compute_ms > 0.5 * total_ms / args.steps else "exchange"}
 
     if args.kernel_only:
@@ -597,6 +630,9 @@ def ours(args, rank, world, local_rank):
     host.close()
     if world > 1:
         e2e = e2e_sharded(args, shard_of, xs, ys, dims, dev, world, barrier, flops_step)
+    gcn_rec = None
+    if args.workload == "cfg2" and not args.no_gcn:
+        gcn_rec = gcn_subrecord(rank, world, dev, barrier)
 
     if rank != 0:
         if world > 1:
@@ -645,6 +681,8 @@ def ours(args, rank, world, local_rank):
             "plan": shard.info(), "preprocess_ms": g.info.get("preprocess_ms")}
     if multi is not None:
         line["multi_gpu"] = multi
+    if gcn_rec is not None:
+        line["gcn"] = gcn_rec
 
     if world == 1:
         ip_h, ix_h, v_h = ip_full_h, ix.cpu().numpy(), v.cpu().numpy()
@@ -661,6 +699,64 @@ def ours(args, rank, world, local_rank):
     else:
         dist.destroy_process_group()
     print(json.dumps(line), flush=True)
+
+
+def gcn_subrecord(rank, world, dev, barrier, workload="cfg5-5m", steps=5):
+    """A short run of the configuration-5 forward (N = 5e6) inside the default line, so that a scaling run of
+    the default workload also carries the forward at every GPU count: ms per forward, the per-layer split,
+    the sampled fp64 check.  `python bench.py --workload cfg5[-5m]` is the full record of the same path."""
+    import torch
+    import torch.distributed as dist
+    from accelgcn import synth, sharded, gcn
+
+    g, ip, ix, v, _dims = build_workload(workload, dev)
+    n, nnz, seed = g.n, int(ix.numel()), g.info["seed"]
+    del g
+    shard = sharded.ShardedSpmm(ip, ix, v, rank, world)
+
+    def x_rows(rows):
+        out = torch.empty((rows.numel(), 128), dtype=torch.float32, device=dev)
+        for a in range(0, rows.numel(), 2_000_000):
+            r = rows[a:a + 2_000_000]
+            base = (r * 128).unsqueeze(1) + torch.arange(128, device=dev, dtype=torch.int64)
+            out[a:a + r.numel()] = synth.uniform_f32_at(seed, 7, base.reshape(-1), -1.0, 1.0).reshape(-1, 128)
+        return out
+    x_block = shard.to_block(x_rows)
+    w1, w2 = synth.glorot(128, 128, seed, 8, dev), synth.glorot(128, 128, seed, 9, dev)
+    fwd = gcn.GcnForward(shard, [w1, w2])
+    out = torch.empty_like(x_block)
+    for _ in range(3):
+        fwd.forward(x_block, out=out)
+    barrier()
+    fwd.status()
+    sampled = gcn_sampled_check(ip, ix, v, x_rows, w1, w2, out, shard.rows_of(), dev, n_sample=16)
+    ok = torch.tensor([1.0 if sampled["ok"] else 0.0], device=dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(steps):
+        fwd.forward(x_block, out=out)
+    e1.record()
+    barrier()
+    parts = torch.tensor(np.asarray(fwd.status(timings=True)).reshape(-1), dtype=torch.float64, device=dev)
+    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(parts, op=dist.ReduceOp.MAX)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    p = parts.tolist()
+    ms = float(t.item()) / steps
+    per_layer = {"gemm": (p[0] + p[3]) / 2, "wait_for_exchange": (p[1] + p[4]) / 2, "spmm_relu": (p[2] + p[5]) / 2}
+    rec = {"workload": f"{workload}: two-layer GCN forward, N={n}, nnz={nnz}, 128 features, through agcn_gcn2_forward_*",
+           "steps": steps, "warmup": 3, "ms_per_forward": ms,
+           "gflops": 2 * (2.0 * nnz * 128 + 2.0 * n * 128 * 128) / ms / 1e6, "per_layer_ms": per_layer,
+           "limiting_phase": max(per_layer.items(), key=lambda kv: kv[1])[0],
+           "exchanged_bytes_in_per_rank_per_layer": 4 * 128 * shard.rows_per_block * (world - 1),
+           "sampled_rows_check_ok_on_every_rank": bool(ok.item() > 0), "sampled_rows_check": sampled,
+           "gpu_launches_per_forward": 2 * (1 + shard.info()["launches_last_step"])}
+    fwd.close()
+    shard.close()
+    return rec
 
 
 def e2e_sharded(args, shard_of, xs, ys, dims, dev, world, barrier, flops_step):
@@ -694,9 +790,8 @@ def e2e_sharded(args, shard_of, xs, ys, dims, dev, world, barrier, flops_step):
     dt = torch.tensor([time.perf_counter() - t0], dtype=torch.float64, device=dev)
     dist.all_reduce(dt, op=dist.ReduceOp.MAX)
     same = all(bool(torch.equal(hy[d], ys[d].cpu())) for d in dims)
-    per = shard_of[dims[0]].rows_per_block
     return {"value": flops_step * reps / float(dt.item()) / 1e9, "unit": UNIT,
-            "h2d_bytes_per_step": sum(4 * d * per for d in dims), "d2h_bytes_per_step": sum(4 * d * per for d in dims),
+            "h2d_bytes_per_step": sum(4 * xs[d].numel() for d in dims), "d2h_bytes_per_step": sum(4 * ys[d].numel() for d in dims),
             "steps": reps, "ms_per_step": float(dt.item()) / reps * 1e3, "bit_identical_to_resident_run": same,
             "call": "per rank: block rows of X up, agcn_dist_gather_begin + agcn_dist_spmm_gathered, block rows of Y down "
                     "(each rank's block of A is resident)"}
@@ -1006,6 +1101,11 @@ def main():
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="cfg2")
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="CPU time spent on the cpu_baseline sample")
     ap.add_argument("--no-ref-gpu", action="store_true", help="skip timing the reference's GPU kernels")
+    ap.add_argument("--feature-groups", type=int, default=0,
+                    help="several GPUs: multiply wide operands as this many independent products of dim / F columns, each "
+                         "row-sharded over world / F ranks (0 = 2 on eight GPUs, else 1)")
+    ap.add_argument("--feature-groups-min-width", type=int, default=32, help="narrowest dim / F that --feature-groups applies to")
+    ap.add_argument("--no-gcn", action="store_true", help="default workload: leave out the short configuration-5 forward (`gcn` record)")
     ap.add_argument("--dim", type=int, default=64, help="dense width of the replicas workload")
     ap.add_argument("--kernel-only", action="store_true", help="resident-data loop only (for profiling under ncu)")
     ap.add_argument("--slices", type=int, default=1,

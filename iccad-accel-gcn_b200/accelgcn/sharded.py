@@ -84,6 +84,18 @@ def exchange_id(rank: int, world: int, group=None) -> bytes | None:
     return box[0]
 
 
+def feature_groups(rank: int, world: int, groups: int):
+    """Rows x features decomposition of a product that is wide enough: the ranks form `groups` feature
+    groups; group j multiplies columns [j * dim / groups, (j + 1) * dim / groups) of the dense operand
+    on a row-sharded A over its own world / groups ranks, with its own communicator.  Every exchange
+    then moves 1 / groups of the columns among world / groups ranks, and a rank's block of A has
+    groups times the rows at 1 / groups of the width.  Returns (row_rank, row_world, feature_group,
+    ranks of this rank's communicator); rank = row_rank * groups + feature_group."""
+    assert groups >= 1 and world % groups == 0, "the number of feature groups must divide the number of ranks"
+    j = rank % groups
+    return rank // groups, world // groups, j, list(range(j, world, groups))
+
+
 class ShardedSpmm:
     """This rank's block of a degree-ordered square A, ready to multiply.
 

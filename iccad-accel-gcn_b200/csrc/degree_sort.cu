@@ -33,7 +33,7 @@ static int degree_sort_device(const int *d_indptr, const int *d_indices, const f
     AGCN_ALLOC(d_flags, scratch, int, 2);   // [0] max degree, [1] error flag
     AGCN_CUDA(cudaMemsetAsync(d_flags, 0, 2 * sizeof(int), s));
 
-    AGCN_KERNEL(degree_keys_kernel, (unsigned)ceil_div(n_rows, 256), 256, s, d_indptr, n_rows, keys_a, rows_a, d_flags, d_flags + 1);
+    AGCN_KERNEL(degree_keys_kernel, (unsigned)ceil_div(n_rows, 256 * KEYS_ITEMS), 256, s, d_indptr, n_rows, keys_a, rows_a, d_flags, d_flags + 1);
     AGCN_LAUNCH_CHECK("degree_keys_kernel");
     int flags[2] = {0, 0}, ends[2] = {0, 0};
     AGCN_CUDA(cudaMemcpyAsync(flags, d_flags, sizeof(flags), cudaMemcpyDeviceToHost, s));

@@ -20,23 +20,42 @@ constexpr int SORT_ITEMS = 16;                       // keys per thread
 constexpr int SORT_TILE = SORT_BLOCK * SORT_ITEMS;   // keys per block
 constexpr int SORT_WARP_KEYS = 32 * SORT_ITEMS;      // contiguous keys owned by one warp
 
-// degree of every row, the identity permutation, and the maximum degree
+// degree of every row, the identity permutation, and the maximum degree; four rows per thread with
+// 16-byte loads and stores where the caller's row pointers are 16-byte aligned
+constexpr int KEYS_ITEMS = 4;
+
 __global__ void __launch_bounds__(256)
 degree_keys_kernel(const int *__restrict__ indptr, int64_t n_rows, unsigned *__restrict__ keys,
                    int *__restrict__ rows, int *__restrict__ max_deg, int *__restrict__ err_flag)
 {
-    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    int d = 0;
-    if (i < n_rows) {
-        d = indptr[i + 1] - indptr[i];
-        if (d < 0) { atomicOr(err_flag, 1); d = 0; }
-        keys[i] = (unsigned)d;
-        rows[i] = (int)i;
+    const int64_t i0 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * KEYS_ITEMS;
+    int d_max = 0;
+    bool negative = false;
+    if (i0 + KEYS_ITEMS <= n_rows && (reinterpret_cast<uintptr_t>(indptr) & 15) == 0) {
+        const int4 a = *reinterpret_cast<const int4 *>(indptr + i0);
+        const int e = indptr[i0 + KEYS_ITEMS];
+        int d[KEYS_ITEMS] = {a.y - a.x, a.z - a.y, a.w - a.z, e - a.w};
+#pragma unroll
+        for (int k = 0; k < KEYS_ITEMS; k++) {
+            if (d[k] < 0) { negative = true; d[k] = 0; }
+            d_max = d_max > d[k] ? d_max : d[k];
+        }
+        *reinterpret_cast<int4 *>(keys + i0) = make_int4(d[0], d[1], d[2], d[3]);      // degrees are >= 0 here
+        *reinterpret_cast<int4 *>(rows + i0) = make_int4((int)i0, (int)i0 + 1, (int)i0 + 2, (int)i0 + 3);
+    } else {
+        for (int64_t i = i0; i < i0 + KEYS_ITEMS && i < n_rows; i++) {
+            int d = indptr[i + 1] - indptr[i];
+            if (d < 0) { negative = true; d = 0; }
+            d_max = d_max > d ? d_max : d;
+            keys[i] = (unsigned)d;
+            rows[i] = (int)i;
+        }
     }
+    if (negative) atomicOr(err_flag, 1);
     // one atomic per block, not per warp: at 5e7 rows a million same-address atomics cost more than the pass
     __shared__ int s_max[256 / 32];
-    d = warp_reduce(d, OpMax());
-    if (lane_id() == 0) s_max[warp_id()] = d;
+    d_max = warp_reduce(d_max, OpMax());
+    if (lane_id() == 0) s_max[warp_id()] = d_max;
     __syncthreads();
     if (threadIdx.x == 0) {
         int m = 0;

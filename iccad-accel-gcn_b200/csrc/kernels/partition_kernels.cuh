@@ -40,11 +40,15 @@ __device__ __forceinline__ int part_warp_nz(int d)
 // Shared-memory view of indptr[tile_first - 1 .. tile_first + PART_TILE + PART_HALO]
 // (indices clamped to [0, n_rows]); deg(i) is valid for tile_first-1 <= i and
 // i < tile_first + PART_TILE + PART_HALO, and returns -1 for rows that do not exist.
+// Every thread walks PART_ITEMS consecutive rows, so the threads of a warp read words PART_ITEMS
+// apart: one pad word per 32 keeps those reads on different banks (unpadded they collide 8 ways).
+__device__ __forceinline__ int part_pad(int k) { return k + (k >> 5); }
+
 struct PartTile {
     int *s_ip;
     int64_t first;    // first row of the tile
     int64_t n_rows;
-    __device__ __forceinline__ int ip(int64_t i) const { return s_ip[i - first + 1]; }
+    __device__ __forceinline__ int ip(int64_t i) const { return s_ip[part_pad((int)(i - first + 1))]; }
     __device__ __forceinline__ int deg(int64_t i) const
     {
         if (i < 0 || i >= n_rows) return -1;
@@ -52,7 +56,8 @@ struct PartTile {
     }
 };
 
-constexpr int PART_SMEM_INTS = PART_TILE + PART_HALO + 2;
+constexpr int PART_TILE_INTS = PART_TILE + PART_HALO + 2;                  // row pointers a tile looks at
+constexpr int PART_SMEM_INTS = PART_TILE_INTS + PART_TILE_INTS / 32 + 1;   // the same, padded
 
 __device__ __forceinline__ PartTile part_load_tile(const int *__restrict__ indptr, int64_t n_rows, int *s_ip)
 {
@@ -60,10 +65,10 @@ __device__ __forceinline__ PartTile part_load_tile(const int *__restrict__ indpt
     t.s_ip = s_ip;
     t.first = (int64_t)blockIdx.x * PART_TILE;
     t.n_rows = n_rows;
-    for (int k = threadIdx.x; k < PART_SMEM_INTS; k += PART_BLOCK) {
+    for (int k = threadIdx.x; k < PART_TILE_INTS; k += PART_BLOCK) {
         int64_t i = t.first - 1 + k;
         i = i < 0 ? 0 : (i > n_rows ? n_rows : i);
-        s_ip[k] = indptr[i];
+        s_ip[part_pad(k)] = indptr[i];
     }
     __syncthreads();
     return t;
