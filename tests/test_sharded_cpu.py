@@ -124,6 +124,48 @@ def test_gloo_sharded_product_equals_single_rank(world, slices, hub, tmp_path):
     assert not np.isnan(y).any() and spmm_close(y, ref, np.full(len(ref), 50.0)).all()
 
 
+def _feature_group_worker(rank, world, port, dim, groups, result_dir):
+    from accelgcn import sharded
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        row_rank, row_world, fgroup, members = sharded.feature_groups(rank, world, groups)
+        assert rank == row_rank * groups + fgroup and members[row_rank] == rank
+        comms = [dist.new_group(ranks=list(range(j, world, groups))) for j in range(groups)]   # every rank makes every group
+        indptr, idx, val = _graph()
+        n, w = len(indptr) - 1, dim // groups
+        x = np.random.default_rng(7).uniform(-1, 1, (n, dim)).astype(np.float32)[:, fgroup * w:(fgroup + 1) * w]
+        ranges, per = sharded.balanced_blocks(indptr, row_world)
+        rows = sharded.block_rows(ranges, per, row_rank)
+        blk = np.zeros((per, w), dtype=np.float32)
+        blk[rows >= 0] = x[rows[rows >= 0]]
+        gathered = torch.zeros((row_world * per, w))
+        dist.all_gather_into_tensor(gathered, torch.from_numpy(blk), group=comms[fgroup])   # among this group's ranks only
+        ip, ix, v = sharded.shard_csr(indptr, idx, val, ranges, per, row_world, 1, row_rank)
+        y = oracle.spmm_block4(oracle.partition(ip), ix, v, gathered.numpy(), per)
+        np.save(os.path.join(result_dir, f"y{rank}.npy"), y)
+        np.save(os.path.join(result_dir, f"rows{rank}.npy"), rows)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_gloo_rows_by_features_product_equals_single_rank(tmp_path):
+    """4 ranks as 2 feature groups x 2 row ranks: each group multiplies its half of the columns on a
+    2-way row-sharded A with its own communicator; the blocks tile Y by rows and columns."""
+    world, groups, dim = 4, 2, 12
+    mp.spawn(_feature_group_worker, args=(world, _free_port(), dim, groups, str(tmp_path)), nprocs=world, join=True)
+    indptr, idx, val = _graph()
+    x = np.random.default_rng(7).uniform(-1, 1, (len(indptr) - 1, dim)).astype(np.float32)
+    ref = oracle.spmm_csr(indptr, idx, val, x)
+    y = np.full_like(ref, np.nan)
+    w = dim // groups
+    for r in range(world):
+        rows, yb = np.load(tmp_path / f"rows{r}.npy"), np.load(tmp_path / f"y{r}.npy")
+        j = r % groups
+        y[rows[rows >= 0], j * w:(j + 1) * w] = yb[rows >= 0]
+    assert not np.isnan(y).any() and spmm_close(y, ref, np.full(len(ref), 50.0)).all()
+
+
 def _failing_worker(rank, world, port, result_dir):
     # rank 1 leaves between steps (no collective of its own in flight); rank 0 must get an error from
     # its next exchange within the process-group timeout instead of waiting forever
