@@ -391,7 +391,7 @@ def ours(args, rank, world, local_rank):
     # own communicator -- 1 / F of the exchange among 1 / F of the ranks, blocks of F times the rows
     fg = 1
     if world > 1:
-        fg = args.feature_groups if args.feature_groups > 0 else (2 if world >= 8 else 1)
+        fg = args.feature_groups if args.feature_groups > 0 else (2 if world % 2 == 0 else 1)
         assert world % fg == 0, "--feature-groups must divide the number of GPUs"
     fg_dims = [d for d in dims if fg > 1 and not sliced and d % fg == 0 and d // fg >= args.feature_groups_min_width]
     shard = sharded.ShardedSpmm(ip, ix, v, rank, world)
@@ -1103,8 +1103,8 @@ def main():
     ap.add_argument("--no-ref-gpu", action="store_true", help="skip timing the reference's GPU kernels")
     ap.add_argument("--feature-groups", type=int, default=0,
                     help="several GPUs: multiply wide operands as this many independent products of dim / F columns, each "
-                         "row-sharded over world / F ranks (0 = 2 on eight GPUs, else 1)")
-    ap.add_argument("--feature-groups-min-width", type=int, default=32, help="narrowest dim / F that --feature-groups applies to")
+                         "row-sharded over world / F ranks (0 = 2 on an even number of GPUs, else 1)")
+    ap.add_argument("--feature-groups-min-width", type=int, default=64, help="narrowest dim / F that --feature-groups applies to")
     ap.add_argument("--no-gcn", action="store_true", help="default workload: leave out the short configuration-5 forward (`gcn` record)")
     ap.add_argument("--dim", type=int, default=64, help="dense width of the replicas workload")
     ap.add_argument("--kernel-only", action="store_true", help="resident-data loop only (for profiling under ncu)")
