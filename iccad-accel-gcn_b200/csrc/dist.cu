@@ -243,9 +243,7 @@ static int dist_set_graph(agcn_dist *d, const int *d_indptr, const int *d_indice
             rc = partition_device(d->indptr, per, d->block4, d->n_blocks, &d->n_blocks, s);
             if (rc != AGCN_OK) return rc;
         }
-        rc = spmm_create(&d->plan, d->block4, d->n_blocks, d->idx, per, d->n_gathered, d->local_nnz, s);
-        if (rc == AGCN_OK && d->world > 1) d->plan->degree_ordered_cols = false;    // gathered positions, block by block
-        return rc;
+        return spmm_create(&d->plan, d->block4, d->n_blocks, d->idx, per, d->n_gathered, d->local_nnz, s);
     }
     // with a sliced exchange the product over a slice starts when that slice has arrived; with column
     // ranges alone every launch gathers from one L2-sized slab of the gathered operand

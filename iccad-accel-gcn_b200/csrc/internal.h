@@ -16,8 +16,6 @@ struct agcn_spmm_plan {
     bool never_split = false;         // set for the ranges of a column-tiled product
     int batch_override = 0;           // AGCN_SPMM_BATCH at creation: 8 or 16 gathers in flight per lane (experiments)
     int pad_unaligned = 1;            // AGCN_SPMM_PAD at creation: copy unaligned X into 16-byte-aligned rows
-    int hot_tail_mb = 0;              // AGCN_SPMM_HOT_MB at creation: MiB of the last rows of X asked to stay in L2 when X >> L2 (0 = all of X)
-    bool degree_ordered_cols = true;  // false where column ids are not in degree order (renamed ids of a row-sharded block)
     float *x_pad = nullptr;           // [n_cols][dim rounded up to 4], grown on demand
     size_t x_pad_bytes = 0;
 };

@@ -28,18 +28,6 @@ __device__ __forceinline__ L2Policies make_l2_policies()
     return p;
 }
 
-// When X is far larger than L2, keeping "all of X" keeps nothing in particular.  The rows that pay are
-// the ones most columns of A point at -- in a degree-ordered symmetric graph the last rows -- so the
-// gather then uses a range policy: loads that fall into the window [hot, hot + bytes) are evict_last,
-// the window has no secondary part, and loads outside it carry no priority of their own.
-__device__ __forceinline__ uint64_t make_l2_hot_range_policy(const void *hot, unsigned bytes)
-{
-    uint64_t policy;
-    asm("createpolicy.range.global.L2::evict_last.L2::evict_first.b64 %0, [%1], %2, %3;"
-        : "=l"(policy) : "l"(hot), "r"(bytes), "r"(bytes));
-    return policy;
-}
-
 // dense operand X: read-only path, 16 bytes per lane, keep in L2
 __device__ __forceinline__ float4 ld_x4(const float *p, uint64_t policy)
 {

@@ -69,9 +69,6 @@ struct SpmmParams {
     int accumulate;           // nonzero: Y += A * X (later column ranges of a column-tiled product)
     int y_vec;                // nonzero: rows of Y are 16-byte aligned and dim_store % 4 == 0
     int dim_store;            // columns of Y written (dim rounded up to 4 is what is gathered)
-    // X far larger than L2: only the window [hot_x, hot_x + hot_bytes) is asked to stay (0: all of X is)
-    const float *hot_x = nullptr;
-    unsigned hot_bytes = 0;
 };
 
 struct TupleView {
@@ -246,8 +243,7 @@ spmm_units_kernel(const SpmmParams p)
     const int slot = lane / LANES, sl = lane % LANES;
     const int col = VEC ? sl * 4 : sl;
     const bool active = col < p.dim;
-    L2Policies pol = make_l2_policies();
-    if (p.hot_bytes != 0) pol.keep = make_l2_hot_range_policy(p.hot_x, p.hot_bytes);
+    const L2Policies pol = make_l2_policies();
 
     if (p.abort_flag != nullptr && *p.abort_flag != 0) return;     // input rejected by a check earlier in the stream
     if ((int64_t)blockIdx.x >= p.n_units) {

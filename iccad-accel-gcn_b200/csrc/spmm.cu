@@ -113,8 +113,6 @@ int spmm_create(agcn_spmm_plan **out, const int *d_block4, int64_t n_blocks, con
         p->panel_override = env_int("AGCN_SPMM_PANEL", 0);
         p->pad_unaligned = env_int("AGCN_SPMM_PAD", 1);
         p->batch_override = env_int("AGCN_SPMM_BATCH", 0);
-        p->hot_tail_mb = env_int("AGCN_SPMM_HOT_MB", 0);
-        if (p->hot_tail_mb > 2048) p->hot_tail_mb = 2048;
     }
     *out = p;
     return AGCN_OK;
@@ -245,22 +243,9 @@ int spmm_run_prepared(agcn_spmm_plan *p, const int *d_indices, const float *d_va
     AGCN_REQUIRE(panel >= 1 && panel <= SPMM_PANEL, "agcn_spmm_run: AGCN_SPMM_PANEL must be 1..%d", SPMM_PANEL);
     if (x_vec && panel % 4 != 0) panel = (panel + 3) & ~3;         // keep every panel's first column 16-byte aligned
     if (panel > SPMM_PANEL) panel = SPMM_PANEL;
-    // X several times larger than L2: ask L2 to keep the rows most nonzeros point at -- the last rows of
-    // a degree-ordered symmetric graph -- instead of all of X (which keeps nothing in particular)
-    const float *hot_x = nullptr;
-    unsigned hot_bytes = 0;
-    if (p->hot_tail_mb > 0 && p->degree_ordered_cols && !accumulate && !p->never_split &&
-        (double)p->n_cols * dim * 4.0 > 1.5 * (double)p->l2_bytes) {
-        const int64_t row_bytes = ldx_use * (int64_t)sizeof(float);
-        int64_t hot_rows = ((int64_t)p->hot_tail_mb << 20) / row_bytes;
-        if (hot_rows > p->n_cols) hot_rows = p->n_cols;
-        hot_x = x_use + (p->n_cols - hot_rows) * ldx_use;
-        hot_bytes = (unsigned)(hot_rows * row_bytes);
-    }
     for (int col0 = 0; col0 < dim; col0 += panel) {
         const int width = dim - col0 < panel ? dim - col0 : panel;
         SpmmParams prm;
-        prm.hot_x = hot_x; prm.hot_bytes = hot_bytes;
         prm.block4 = p->block4; prm.n_blocks = p->n_blocks;
         prm.n_units = unit1 - unit0; prm.unit_base = unit0; prm.abort_flag = part.abort_flag;
         prm.idx = d_indices; prm.val = d_vals;
