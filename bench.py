@@ -761,23 +761,33 @@ def gcn_subrecord(rank, world, dev, barrier, workload="cfg5-5m", steps=5):
 
 def e2e_sharded(args, shard_of, xs, ys, dims, dev, world, barrier, flops_step):
     """End to end on several GPUs: every rank's block rows of X go up from pinned host memory, the
-    step (exchange + products) runs, its block rows of Y come down -- all inside the timed region."""
+    step (exchange + products) runs, its block rows of Y come down -- all inside the timed region.
+    Three streams: each upload is followed, on the upload stream, by the start of its exchange; the
+    products run on the current stream, each waiting for its own operand only; every result goes down
+    on a third stream while the next product runs."""
     import torch
     import torch.distributed as dist
     hx = {d: xs[d].cpu().pin_memory() for d in dims}
     hy = {d: torch.empty(tuple(ys[d].shape), dtype=torch.float32).pin_memory() for d in dims}
     xd = {d: torch.empty_like(xs[d]) for d in dims}
+    cur = torch.cuda.current_stream(dev)
+    s_up, s_down = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    done = {d: torch.cuda.Event() for d in dims}
 
     def step():
-        for d in dims:
-            xd[d].copy_(hx[d], non_blocking=True)
         for g0 in range(0, len(dims), 4):
             group = list(enumerate(dims))[g0:g0 + 4]
+            s_up.wait_stream(cur)                   # the slots' previous readers are behind this point
+            with torch.cuda.stream(s_up):
+                for di, d in group:
+                    xd[d].copy_(hx[d], non_blocking=True)
+                    shard_of[d].gather_begin(xd[d], slot=di % 4, stream=s_up)
             for di, d in group:
-                shard_of[d].gather_begin(xd[d], slot=di % 4)
-            for di, d in group:
-                shard_of[d].multiply(ys[d], slot=di % 4)
-                hy[d].copy_(ys[d], non_blocking=True)
+                shard_of[d].multiply(ys[d], slot=di % 4, stream=cur)
+                done[d].record(cur)
+                s_down.wait_event(done[d])
+                with torch.cuda.stream(s_down):
+                    hy[d].copy_(ys[d], non_blocking=True)
         torch.cuda.synchronize(dev)
 
     reps = max(1, min(args.steps, 5))
@@ -794,7 +804,7 @@ def e2e_sharded(args, shard_of, xs, ys, dims, dev, world, barrier, flops_step):
             "h2d_bytes_per_step": sum(4 * xs[d].numel() for d in dims), "d2h_bytes_per_step": sum(4 * ys[d].numel() for d in dims),
             "steps": reps, "ms_per_step": float(dt.item()) / reps * 1e3, "bit_identical_to_resident_run": same,
             "call": "per rank: block rows of X up, agcn_dist_gather_begin + agcn_dist_spmm_gathered, block rows of Y down "
-                    "(each rank's block of A is resident)"}
+                    "(each rank's block of A is resident); uploads, products and downloads on three streams"}
 
 
 def ours_gcn(args, rank, world, local_rank):

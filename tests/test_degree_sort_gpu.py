@@ -97,3 +97,22 @@ def test_values_given_but_not_wanted_and_wrong_nnz():
                                          perm.data_ptr(), nip.data_ptr(), nix.data_ptr(), None, None)
         assert rc == _lib.ERR_INVALID and b"nnz" in lib.agcn_last_error()
     torch.cuda.synchronize()
+
+
+def test_row_pointers_at_any_alignment():
+    # the degree pass reads four row pointers per 16-byte load where the caller's array allows it and
+    # one at a time where it does not: the same matrix through pointers at offsets 0..3 words
+    import torch
+    from accelgcn import degree_sort, synth
+    dev = require_cuda()
+    g = synth.make_config(1, "cpu", 0.5)
+    want = oracle.degree_sort(g.indptr.numpy(), g.indices.numpy(), None, True)
+    ix = g.indices.to(dev)
+    for shift in range(4):
+        buf = torch.zeros(g.n + 1 + shift, dtype=torch.int32, device=dev)
+        buf[shift:] = g.indptr.to(dev)
+        view = buf[shift:]
+        assert view.data_ptr() % 16 == (4 * shift) % 16
+        perm, nip, nix, _ = degree_sort.degree_sort_device(view, ix, None, relabel_cols=True)
+        assert np.array_equal(perm.cpu().numpy(), want[0]), shift
+        assert np.array_equal(nip.cpu().numpy(), want[1]) and np.array_equal(nix.cpu().numpy(), want[2]), shift
