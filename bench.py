@@ -401,7 +401,6 @@ def ours(args, rank, world, local_rank):
     lib = _lib.load()
     if sliced and any(d >= args.slices_min_dim for d in dims):
         shard_sliced = sharded.ShardedSpmm(ip, ix, v, rank, world, exchange_slices=args.slices)
-        assert shard_sliced.rows_per_block == shard.rows_per_block, "--slices must divide the block height"
         shard_of.update({d: shard_sliced for d in dims if d >= args.slices_min_dim})
     elif world > 1 and args.tiled != "off":
         # a gathered operand that does not fit L2 is multiplied column range by column range (as on one GPU):
