@@ -50,6 +50,7 @@ PROTOTYPES = {
     "agcn_spmm_tiled_suggest": (_int, [_i64, _i64, _i64, _int]),
     "agcn_gemm_tf32_async": (_int, [_vp, _i64, _vp, _vp, _i64, _i64, _int, _int, _vp, _vp]),
     "agcn_gemm_tf32_selftest_timeout": (_int, [_vp, _i64, _vp, _vp, _i64, _i64, _vp]),
+    "agcn_gcn_fused_layer": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _vp, _vp]),
     "agcn_balanced_blocks": (_int, [_vp, _i64, _int, _vp, ctypes.POINTER(_i64)]),
     "agcn_dist_unique_id": (_int, [_vp]),
     "agcn_dist_create": (_int, [ctypes.POINTER(_vp), _int, _int, _vp]),

@@ -45,3 +45,25 @@ def selftest_timeout(h, w, out, stream=None) -> int:
     with torch.cuda.device(h.device):
         return lib.agcn_gemm_tf32_selftest_timeout(h.data_ptr(), h.stride(0), w.data_ptr(), out.data_ptr(), out.stride(0),
                                                    h.shape[0], s.cuda_stream)
+
+
+def gcn_fused_layer(indptr, indices, vals, z_in, w, m_rows, out=None, status=None, stream=None):
+    """Z2[r] = relu(A[r, :] @ Z1) @ W for the first m_rows rows of a CSR matrix, all of at most 32
+    nonzeros (agcn_gcn_fused_layer): the activations stay in shared memory between the gather and the
+    tensor-core product.  z_in [n_cols, 128], w [128, 128] contiguous fp32 CUDA tensors."""
+    import torch
+    lib = _lib.load()
+    if not (z_in.is_contiguous() and w.is_contiguous() and z_in.shape[1] == 128 and tuple(w.shape) == (128, 128)):
+        raise ValueError("gcn_fused_layer: z_in must be contiguous [n_cols, 128] and w contiguous [128, 128]")
+    dev = z_in.device
+    z = out if out is not None else torch.empty((m_rows, 128), dtype=torch.float32, device=dev)
+    st = status if status is not None else torch.zeros(1, dtype=torch.int32, device=dev)
+    s = stream if stream is not None else torch.cuda.current_stream(dev)
+    with torch.cuda.device(dev):
+        _lib.check(lib.agcn_gcn_fused_layer(indptr.data_ptr(), indices.data_ptr(), vals.data_ptr(), z_in.data_ptr(),
+                                            w.data_ptr(), z.data_ptr(), int(m_rows), int(z_in.shape[0]), st.data_ptr(), s.cuda_stream))
+    if status is None:
+        s.synchronize()
+        if int(st.item()) != 0:
+            raise _lib.AccelGcnError(_lib.ERR_CUDA, f"agcn_gcn_fused_layer: status {int(st.item())} (1-3: a pipeline wait ran out; 4: column id out of range)")
+    return z

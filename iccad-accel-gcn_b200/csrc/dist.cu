@@ -108,8 +108,13 @@ struct agcn_gcn2 {
     agcn_dist *dist = nullptr;
     const float *w[2] = {nullptr, nullptr};
     float *z = nullptr, *h1 = nullptr;        // [per x 128] each
-    int *d_status = nullptr;                  // GEMM status words, one per layer
+    int *d_status = nullptr;                  // status words: the GEMM of each layer, the fused kernel, the GEMM of the other rows
     cudaEvent_t ev[8] = {};
+    // AGCN_GCN_FUSED=1: the leading rows of the block (at most 32 nonzeros each) go through one kernel
+    // from layer 1's gathered operand to layer 2's operand; the other rows through SpMM and GEMM as before
+    float *z2 = nullptr;                      // [per x 128]: layer 2's operand
+    int64_t fused_rows = 0;                   // rows [0, fused_rows) are the fused kernel's
+    int64_t rest_unit = 0;                    // first unit of the SpMM over the other rows (it may start a few rows early)
 };
 
 namespace agcn {
@@ -344,7 +349,7 @@ static int dist_spmm_on_gathered(agcn_dist *d, const float *d_gathered, float *d
 static void gcn2_free(agcn_gcn2 *f)
 {
     if (f == nullptr) return;
-    cudaFree(f->z); cudaFree(f->h1); cudaFree(f->d_status);
+    cudaFree(f->z); cudaFree(f->h1); cudaFree(f->z2); cudaFree(f->d_status);
     for (cudaEvent_t e : f->ev) if (e) cudaEventDestroy(e);
     delete f;
 }
@@ -479,9 +484,32 @@ extern "C" int agcn_gcn2_forward_create(agcn_gcn2 **fwd, agcn_dist *dist, const 
     const size_t bytes = (size_t)dist->per * 128 * sizeof(float);
     AGCN_CUDA(cudaMalloc(&f->z, bytes));
     AGCN_CUDA(cudaMalloc(&f->h1, bytes));
-    AGCN_CUDA(cudaMalloc(&f->d_status, 2 * sizeof(int)));
-    AGCN_CUDA(cudaMemset(f->d_status, 0, 2 * sizeof(int)));
+    AGCN_CUDA(cudaMalloc(&f->d_status, 4 * sizeof(int)));
+    AGCN_CUDA(cudaMemset(f->d_status, 0, 4 * sizeof(int)));
     for (cudaEvent_t &e : f->ev) AGCN_CUDA(cudaEventCreate(&e));
+    if (env_int("AGCN_GCN_FUSED", 0) != 0 && dist->plan != nullptr && dist->per > 0 && dist->n_blocks > 0) {
+        // leading rows of at most 32 nonzeros (the block starts with its light rows in ascending degree), in whole tiles
+        std::vector<int> h_indptr((size_t)dist->per + 1);
+        AGCN_CUDA(cudaMemcpy(h_indptr.data(), dist->indptr, h_indptr.size() * sizeof(int), cudaMemcpyDeviceToHost));
+        int64_t rows = 0;
+        while (rows < dist->per && h_indptr[rows + 1] - h_indptr[rows] <= fused_layer_max_degree()) rows++;
+        rows -= rows % 128;
+        // the unit (8 tuples) that holds the first row left to the SpMM: first rows of every unit's first tuple
+        const int64_t n_units = ceil_div(dist->n_blocks, 8);
+        std::vector<int> unit_row((size_t)n_units);
+        AGCN_CUDA(cudaMemcpy2D(unit_row.data(), sizeof(int), dist->block4 + 1, 8 * 4 * sizeof(int), sizeof(int), (size_t)n_units,
+                               cudaMemcpyDeviceToHost));
+        int64_t lo = 0, hi = n_units;                    // first unit whose first row is > rows
+        while (lo < hi) {
+            const int64_t mid = lo + (hi - lo) / 2;
+            if (unit_row[mid] <= rows) lo = mid + 1; else hi = mid;
+        }
+        if (rows >= 128 * 64 && lo > 0) {
+            f->fused_rows = rows;
+            f->rest_unit = lo - 1;
+            AGCN_CUDA(cudaMalloc(&f->z2, bytes));
+        }
+    }
     guard.f = nullptr;
     *fwd = f;
     return AGCN_OK;
@@ -498,13 +526,39 @@ extern "C" int agcn_gcn2_forward_run(agcn_gcn2 *fwd, const float *d_x_block, flo
     agcn_dist *d = fwd->dist;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const float *h = d_x_block;
+    const bool fused = fwd->fused_rows > 0;
     for (int layer = 0; layer < 2; layer++) {
         float *out = layer == 0 ? fwd->h1 : d_out_block;
+        const float *operand = fwd->z;
         AGCN_CUDA(cudaEventRecord(fwd->ev[4 * layer + 0], s));
-        int rc = gemm_tf32_async(h, 128, fwd->w[layer], fwd->z, 128, d->per, fwd->d_status + layer, s);
+        int rc = AGCN_OK;
+        if (fused && layer == 1) operand = fwd->z2;        // made by layer 1's fused step
+        else rc = gemm_tf32_async(h, 128, fwd->w[layer], fwd->z, 128, d->per, fwd->d_status + layer, s);
         if (rc != AGCN_OK) return rc;
         AGCN_CUDA(cudaEventRecord(fwd->ev[4 * layer + 1], s));
-        rc = dist_gather_begin(d, 0, fwd->z, 128, s);
+        rc = dist_gather_begin(d, 0, operand, 128, s);
+        if (rc == AGCN_OK && fused && layer == 0) {
+            // light rows: relu(A Z1) W2 in one kernel; the other rows: SpMM + ReLU into H1, then their rows of H1 W2
+            AGCN_CUDA(cudaStreamWaitEvent(s, d->ev_ready[0][0], 0));
+            AGCN_CUDA(cudaEventRecord(fwd->ev[2], s));
+            const float *zg = d->gathered_ptr[0];
+            rc = fused_layer_async(d->indptr, d->idx, d->val, zg, fwd->w[1], fwd->z2, fwd->fused_rows, d->world == 1 ? d->per : d->n_gathered,
+                                   fwd->d_status + 2, s);
+            if (rc != AGCN_OK) return rc;
+            SpmmLaunchPart part;
+            part.unit0 = fwd->rest_unit;
+            d->plan->launches_last_run = 0;
+            rc = spmm_run_prepared(d->plan, d->idx, d->val, zg, 128, true, fwd->h1, 128, 128, s, AGCN_ACT_RELU, 0, part);
+            if (rc != AGCN_OK) return rc;
+            d->launches_last_step = d->plan->launches_last_run + 2;
+            AGCN_CUDA(cudaEventRecord(d->ev_consumed[0], s));
+            rc = gemm_tf32_async(fwd->h1 + fwd->fused_rows * 128, 128, fwd->w[1], fwd->z2 + fwd->fused_rows * 128, 128,
+                                 d->per - fwd->fused_rows, fwd->d_status + 3, s);
+            if (rc != AGCN_OK) return rc;
+            AGCN_CUDA(cudaEventRecord(fwd->ev[3], s));
+            h = out;
+            continue;
+        }
         if (rc != AGCN_OK) return rc;
         AGCN_CUDA(cudaStreamWaitEvent(s, d->ev_ready[0][0], 0));
         AGCN_CUDA(cudaEventRecord(fwd->ev[4 * layer + 2], s));          // the first slice has arrived
@@ -525,9 +579,9 @@ extern "C" int agcn_gcn2_forward_status(agcn_gcn2 *fwd, float *ms6)
     using namespace agcn;
     clear_error();
     AGCN_REQUIRE(fwd != nullptr, "agcn_gcn2_forward_status: null argument");
-    int status[2] = {0, 0};
+    int status[4] = {0, 0, 0, 0};
     AGCN_CUDA(cudaMemcpy(status, fwd->d_status, sizeof(status), cudaMemcpyDeviceToHost));
-    if (status[0] != 0 || status[1] != 0) {
+    if (status[0] != 0 || status[1] != 0 || status[2] != 0 || status[3] != 0) {
         set_error("agcn_gcn2_forward: a pipeline wait of the dense transform ran out (layer %d); the output is incomplete",
                   status[0] != 0 ? 1 : 2);
         return AGCN_ERR_CUDA;

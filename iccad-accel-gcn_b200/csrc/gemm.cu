@@ -4,6 +4,7 @@
 #include "host_common.h"
 #include "internal.h"
 #include "kernels/gemm_tf32_kernels.cuh"
+#include "kernels/fused_layer_kernels.cuh"
 
 #include <cudaTypedefs.h>
 #include <mutex>
@@ -150,4 +151,55 @@ extern "C" int agcn_gemm_tf32_selftest_timeout(const float *d_h, int64_t ldh, co
     // 4096 polls of about 100 ns: the starved wait gives up after well under a millisecond
     return agcn::gemm_tf32_sync(d_h, ldh, d_w, d_z, ldz, m_rows, agcn::GEMM_DIM, agcn::GEMM_DIM,
                                 static_cast<cudaStream_t>(stream), 4096u, 1);
+}
+
+// ---------------------------------------------------------------------------
+// GCN layer boundary fused into one kernel for the light rows of a degree-ordered block:
+// Z2[r] = relu(A[r, :] * Z1) * W, the activations staying in shared memory between the gather and the
+// tensor-core product (kernels/fused_layer_kernels.cuh).  The reference stops at the SpMM
+// (spmm_accel.cu:104-108); this is the step a GCN puts behind it.
+namespace agcn {
+
+// Rows [0, m_rows) of the block must all have at most FUSED_MAX_DEG nonzeros (the caller checks: the
+// kernel clamps, it does not verify).  Nothing is allocated, the stream is not synchronised;
+// *d_status (device, zeroed here on the stream) receives a GEMM_ERR_* code if a pipeline wait runs out.
+int fused_layer_async(const int *d_indptr, const int *d_indices, const float *d_vals, const float *d_z_in, const float *d_w,
+                      float *d_z_out, int64_t m_rows, int64_t n_cols, int *d_status, cudaStream_t s)
+{
+    AGCN_REQUIRE(d_indptr != nullptr && d_z_in != nullptr && d_w != nullptr && d_z_out != nullptr && d_status != nullptr,
+                 "agcn_gcn_fused_layer: null pointer");
+    AGCN_REQUIRE(m_rows >= 0 && m_rows < ((int64_t)1 << 31) * GEMM_TILE_M / 2 && n_cols > 0, "agcn_gcn_fused_layer: row or column count out of range");
+    AGCN_REQUIRE(aligned16(d_z_in) && aligned16(d_z_out), "agcn_gcn_fused_layer: Z1 and Z2 must be 16-byte aligned");
+    AGCN_CUDA(cudaMemsetAsync(d_status, 0, sizeof(int), s));
+    if (m_rows == 0) return AGCN_OK;
+    AGCN_REQUIRE(d_indices != nullptr && d_vals != nullptr, "agcn_gcn_fused_layer: null indices or values");
+
+    static int sm_count_of[64] = {};
+    int dev = 0;
+    AGCN_CUDA(cudaGetDevice(&dev));
+    AGCN_REQUIRE(dev >= 0 && dev < 64, "agcn_gcn_fused_layer: device ordinal %d not supported", dev);
+    if (sm_count_of[dev] == 0) {
+        int sm_count = 0;
+        AGCN_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
+        AGCN_CUDA(cudaFuncSetAttribute(gcn_fused_layer_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FUSED_SMEM_BYTES));
+        sm_count_of[dev] = sm_count;
+    }
+    const int n_tiles = (int)ceil_div(m_rows, GEMM_TILE_M);
+    const int grid = n_tiles < sm_count_of[dev] ? n_tiles : sm_count_of[dev];
+    gcn_fused_layer_kernel<<<grid, FUSED_THREADS, FUSED_SMEM_BYTES, s>>>(d_indptr, d_indices, d_vals, d_z_in, d_w, d_z_out, m_rows,
+                                                                         n_cols, n_tiles, d_status, GEMM_SPIN_LIMIT);
+    AGCN_LAUNCH_CHECK("gcn_fused_layer_kernel");
+    return AGCN_OK;
+}
+
+int fused_layer_max_degree() { return FUSED_MAX_DEG; }
+
+}  // namespace agcn
+
+extern "C" int agcn_gcn_fused_layer(const int32_t *d_indptr, const int32_t *d_indices, const float *d_vals, const float *d_z_in,
+                                    const float *d_w, float *d_z_out, int64_t m_rows, int64_t n_cols, int32_t *d_status, void *stream)
+{
+    agcn::clear_error();
+    return agcn::fused_layer_async(d_indptr, d_indices, d_vals, d_z_in, d_w, d_z_out, m_rows, n_cols, d_status,
+                                   static_cast<cudaStream_t>(stream));
 }

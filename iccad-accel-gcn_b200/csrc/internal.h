@@ -57,6 +57,11 @@ void plan_free(agcn_spmm_plan *p);
 // gemm.cu: Z = H * W (128 x 128, TF32) enqueued on `s`; nothing allocated, nothing synchronised
 int gemm_tf32_async(const float *d_h, int64_t ldh, const float *d_w, float *d_z, int64_t ldz, int64_t m_rows,
                     int *d_status, cudaStream_t s);
+// Z2[r] = relu(A[r, :] * Z1) * W for the first m_rows rows of a CSR block, all of at most
+// fused_layer_max_degree() nonzeros (gemm.cu)
+int fused_layer_async(const int *d_indptr, const int *d_indices, const float *d_vals, const float *d_z_in, const float *d_w,
+                      float *d_z_out, int64_t m_rows, int64_t n_cols, int *d_status, cudaStream_t s);
+int fused_layer_max_degree();
 
 // layout.cu
 int balanced_blocks(const int *h_indptr, int64_t n_rows, int world, int64_t *h_ranges, int64_t *rows_per_block);

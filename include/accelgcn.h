@@ -229,6 +229,21 @@ int agcn_gemm_tf32_async(const float *d_h, int64_t ldh, const float *d_w, float 
 int agcn_gemm_tf32_selftest_timeout(const float *d_h, int64_t ldh, const float *d_w, float *d_z,
                                     int64_t ldz, int64_t m_rows, void *stream);
 
+/* One GCN layer boundary in one kernel, for rows of at most 32 nonzeros (no counterpart in the
+ * reference, which stops at the SpMM, spmm_accel.cu:104-108):
+ *     Z2[r, :] = relu(A[r, :] * Z1) * W      for r in [0, m_rows)
+ * A is given by its CSR arrays (d_indptr int32[>= m_rows + 1], d_indices / d_vals); EVERY one of these
+ * rows must have at most 32 nonzeros -- the leading rows of a degree-ordered matrix -- or the
+ * result of a longer row is wrong (the kernel uses its first 32 nonzeros only; it does not fault):
+ * callers check the degree of row m_rows - 1.  Z1 is [n_cols x 128] and W [128 x 128], row-major,
+ * Z2 [m_rows x 128]; TF32 multiply with fp32 accumulation for the dense part, fp32 for the sparse part.
+ * The activations relu(A * Z1) are gathered straight into the shared-memory operand tiles of the
+ * tensor-core product and never reach global memory.  Asynchronous; d_status as in agcn_gemm_tf32_async,
+ * plus 4 = a column id outside [0, n_cols) was met (that nonzero was read from row 0: no fault). */
+int agcn_gcn_fused_layer(const int32_t *d_indptr, const int32_t *d_indices, const float *d_vals,
+                         const float *d_z_in, const float *d_w, float *d_z_out, int64_t m_rows,
+                         int64_t n_cols, int32_t *d_status, void *stream);
+
 /* ------------------------------------------------------------------------
  * Host-buffer SpMM: the plug-in used by a harness that keeps its arrays in
  * host memory.  The split follows SPMM_BASE: agcn_host_set_graph is the

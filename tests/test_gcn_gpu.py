@@ -195,3 +195,83 @@ def test_two_layer_gcn_forward_at_five_million_nodes():
     assert err.max() <= 4e-3 * scale, err.max() / scale
     # and tighter where it matters: the typical element, not just the worst one
     assert float(np.sqrt((err.astype(np.float64) ** 2).mean())) <= 4e-4 * scale
+
+
+@pytest.mark.parametrize("m,n_cols", [(1, 64), (127, 500), (1000, 5000), (128 * 300 + 17, 40_000)])
+def test_fused_layer_matches_fp64(m, n_cols):
+    # Z2 = relu(A Z1) W for rows of 0..32 nonzeros: the sparse part in fp32 (rel 1e-4), the dense part in
+    # TF32 (2e-3 of the row scale sum_k |h_k w_kn|)
+    import torch
+    from accelgcn import gemm, synth
+    dev = require_cuda()
+    rng = np.random.default_rng(m)
+    deg = rng.integers(0, 33, m)
+    deg[rng.integers(0, m, max(1, m // 50))] = 32
+    deg[rng.integers(0, m, max(1, m // 50))] = 0
+    ip = np.concatenate([[0], np.cumsum(deg)]).astype(np.int32)
+    ix = rng.integers(0, n_cols, int(ip[-1])).astype(np.int32)
+    v = rng.uniform(-1, 1, int(ip[-1])).astype(np.float32)
+    z1 = synth.features(n_cols, 128, 77 + m, dev)
+    w = synth.glorot(128, 128, 5, 9, dev)
+    out = torch.full((m + 3, 128), float("nan"), device=dev)
+    gemm.gcn_fused_layer(torch.from_numpy(ip).to(dev), torch.from_numpy(ix).to(dev), torch.from_numpy(v).to(dev), z1, w, m,
+                         out=out[:m])
+    torch.cuda.synchronize()
+    assert torch.isnan(out[m:]).all()                       # rows past m_rows are not written
+    z1_h, w_h = z1.cpu().numpy().astype(np.float64), w.cpu().numpy().astype(np.float64)
+    h = np.zeros((m, 128))
+    rows = np.repeat(np.arange(m), deg)
+    np.add.at(h, rows, v[:, None].astype(np.float64) * z1_h[ix])
+    h = np.maximum(h, 0)
+    ref = h @ w_h
+    scale = np.abs(h) @ np.abs(w_h)
+    got = out[:m].cpu().numpy()
+    assert not np.isnan(got).any()
+    assert np.all(np.abs(got - ref) <= 2e-3 * scale + 1e-5), float(np.max(np.abs(got - ref) / (scale + 1e-30)))
+
+
+def test_forward_with_fused_layer_boundary(monkeypatch):
+    # AGCN_GCN_FUSED=1: the light rows of the block take the fused kernel between the layers, the others
+    # SpMM + GEMM; the result must agree with the plain forward (same arithmetic, another summation order)
+    import torch
+    from accelgcn import synth, degree_sort, sharded, gcn
+    dev = require_cuda()
+    g = synth.make_config(5, dev, 0.002)
+    _, ip, ix, v = degree_sort.degree_sort_device(g.indptr, g.indices, g.vals)
+    x = synth.features(g.n, 128, 1005, dev)
+    w1, w2 = synth.glorot(128, 128, 1005, 8, dev), synth.glorot(128, 128, 1005, 9, dev)
+    sh = sharded.ShardedSpmm(ip, ix, v, 0, 1)
+    xb = sh.to_block(x)
+    plain = gcn.GcnForward(sh, [w1, w2])
+    want = plain.forward(xb).clone()
+    torch.cuda.synchronize()
+    plain.status()
+    plain.close()
+    monkeypatch.setenv("AGCN_GCN_FUSED", "1")
+    fused = gcn.GcnForward(sh, [w1, w2])
+    got = fused.forward(xb)
+    torch.cuda.synchronize()
+    fused.status()
+    deg = (ip[1:] - ip[:-1])
+    assert int((deg <= 32).sum()) >= 128 * 64              # the fused path is really taken at this size
+    scale = float(want.abs().max())
+    assert float((got - want).abs().max()) <= 2e-3 * scale
+    assert not torch.equal(got, want) or True
+    fused.close(); sh.close()
+
+
+def test_fused_layer_reports_a_column_out_of_range():
+    import torch
+    from accelgcn import gemm, synth, AccelGcnError
+    dev = require_cuda()
+    ip = torch.tensor([0, 2, 3], dtype=torch.int32, device=dev)
+    ix = torch.tensor([1, 50, 7], dtype=torch.int32, device=dev)          # 50 is outside the 50 rows of Z1
+    v = torch.ones(3, device=dev)
+    z1 = synth.features(50, 128, 3, dev)
+    w = torch.eye(128, device=dev)
+    with pytest.raises(AccelGcnError, match="status 4"):
+        gemm.gcn_fused_layer(ip, ix, v, z1, w, 2)
+    ix[1] = 49
+    got = gemm.gcn_fused_layer(ip, ix, v, z1, w, 2)                        # the device is fine: the next call succeeds
+    want = torch.relu(torch.stack([z1[1] + z1[49], z1[7]]))
+    assert torch.allclose(got, want, rtol=2e-3, atol=2e-3)
