@@ -206,8 +206,8 @@ def test_fused_layer_matches_fp64(m, n_cols):
     dev = require_cuda()
     rng = np.random.default_rng(m)
     deg = rng.integers(0, 33, m)
-    deg[rng.integers(0, m, max(1, m // 50))] = 32
     deg[rng.integers(0, m, max(1, m // 50))] = 0
+    deg[rng.integers(0, m, max(1, m // 50))] = 32
     ip = np.concatenate([[0], np.cumsum(deg)]).astype(np.int32)
     ix = rng.integers(0, n_cols, int(ip[-1])).astype(np.int32)
     v = rng.uniform(-1, 1, int(ip[-1])).astype(np.float32)
@@ -256,7 +256,6 @@ def test_forward_with_fused_layer_boundary(monkeypatch):
     assert int((deg <= 32).sum()) >= 128 * 64              # the fused path is really taken at this size
     scale = float(want.abs().max())
     assert float((got - want).abs().max()) <= 2e-3 * scale
-    assert not torch.equal(got, want) or True
     fused.close(); sh.close()
 
 
