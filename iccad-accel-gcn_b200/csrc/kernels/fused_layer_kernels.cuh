@@ -6,13 +6,20 @@
 // gemm_tf32_128_kernel.
 //
 //   persistent CTAs, one per SM, each taking tiles of 128 rows round-robin;
-//   warps 0, 6-15      producers: every warp gathers FUSED_ROWS rows at a time (the rows' column ids
+//   warps 0, 6-31      producers: every warp gathers FUSED_ROWS rows at a time (the rows' column ids
 //                      and values sit in the lanes' registers and are broadcast by shuffle; a lane
-//                      owns 4 of the 128 columns), 16 loads of 16 bytes in flight per lane;
+//                      owns 4 of the 128 columns), 8 loads of 16 bytes in flight per lane;
 //   warp 1 (one lane)  MMA issuer;   warps 2-5  epilogue.
 //   The operand ring holds two tiles of four K-blocks; a tile's four stage barriers are arrived on
 //   by every producer warp once its rows of the tile are written and fenced for the async proxy.
 // Every wait is bounded, as in the GEMM.
+//
+// Measured on B200 (two-layer forward, N = 5e6): correct, and slower than SpMM + GEMM -- 26.0 ms per
+// forward against 14.3 ms.  One thread block per SM (192 KiB of operand tiles and W) leaves the gather
+// 27 warps of 8 loads each where the stand-alone SpMM has 40 warps, every one of them with its own
+// chain of dependent rounds (row pointers, column ids, gathers), and the dense transform it saves is
+// 6 % of the forward.  It is therefore off by default (AGCN_GCN_FUSED=1 turns it on in
+// agcn_gcn2_forward_*) and kept as the measured variant.
 #pragma once
 #include "gemm_tf32_kernels.cuh"
 #include "ptx.cuh"
@@ -20,10 +27,10 @@
 namespace agcn {
 
 constexpr int FUSED_STAGES = 2 * GEMM_KBLKS;          // two operand tiles
-constexpr int FUSED_PROD_WARPS = 11;
-constexpr int FUSED_WARPS = 2 + GEMM_EPI_WARPS + FUSED_PROD_WARPS - 1;   // warp 0 is a producer too: 16 warps
+constexpr int FUSED_PROD_WARPS = 27;
+constexpr int FUSED_WARPS = 2 + GEMM_EPI_WARPS + FUSED_PROD_WARPS - 1;   // warp 0 is a producer too: 32 warps
 constexpr int FUSED_THREADS = 32 * FUSED_WARPS;
-constexpr int FUSED_ROWS = 4;                         // rows a producer warp gathers at a time
+constexpr int FUSED_ROWS = 2;                         // rows a producer warp gathers at a time
 constexpr int FUSED_MAX_DEG = 32;                     // nonzeros of a row live in one register per lane
 constexpr int FUSED_ERR_BAD_COLUMN = 4;               // status code beside the GEMM_ERR_TIMEOUT_* ones
 constexpr int FUSED_SMEM_BYTES = 1024 /* alignment slack */ + GEMM_W_BYTES + FUSED_STAGES * GEMM_STAGE_BYTES +
@@ -179,25 +186,27 @@ gcn_fused_layer_kernel(const int *__restrict__ indptr, const int *__restrict__ i
 #pragma unroll
                 for (int q = 0; q < FUSED_ROWS; q++) acc[q] = make_float4(0.f, 0.f, 0.f, 0.f);
                 for (int i = 0; i < max_cnt; i += 4) {
+                    // no branch around a load: a slot past the end of its row reads row 0 and is then zeroed
                     float4 v[FUSED_ROWS][4];
 #pragma unroll
                     for (int q = 0; q < FUSED_ROWS; q++)
 #pragma unroll
                         for (int u = 0; u < 4; u++) {
-                            int col = __shfl_sync(0xffffffffu, pc[q], (i + u) & 31);
-                            if ((uint64_t)(int64_t)col >= (uint64_t)n_cols) { bad_column = bad_column || i + u < cnt[q]; col = 0; }
-                            v[q][u] = i + u < cnt[q] ? ld_x4(z_in + (int64_t)col * GEMM_DIM + 4 * lane, pol.keep)
-                                                     : make_float4(0.f, 0.f, 0.f, 0.f);
+                            int col = __shfl_sync(0xffffffffu, pc[q], (i + u) & 31);       // 0 from the lanes past the row's end
+                            const bool outside = (uint64_t)(int64_t)col >= (uint64_t)n_cols;
+                            bad_column = bad_column || outside;
+                            col = outside ? 0 : col;
+                            v[q][u] = ld_x4(z_in + (int64_t)col * GEMM_DIM + 4 * lane, pol.keep);
                         }
 #pragma unroll
                     for (int q = 0; q < FUSED_ROWS; q++)
 #pragma unroll
                         for (int u = 0; u < 4; u++) {
-                            const float a = __shfl_sync(0xffffffffu, pv[q], (i + u) & 31);
-                            if (i + u < cnt[q]) {
-                                acc[q].x = fmaf(a, v[q][u].x, acc[q].x); acc[q].y = fmaf(a, v[q][u].y, acc[q].y);
-                                acc[q].z = fmaf(a, v[q][u].z, acc[q].z); acc[q].w = fmaf(a, v[q][u].w, acc[q].w);
-                            }
+                            const bool live = i + u < cnt[q];
+                            const float a = __shfl_sync(0xffffffffu, pv[q], (i + u) & 31);       // 0 past the row's end
+                            const float4 x = v[q][u];
+                            acc[q].x = fmaf(a, live ? x.x : 0.f, acc[q].x); acc[q].y = fmaf(a, live ? x.y : 0.f, acc[q].y);
+                            acc[q].z = fmaf(a, live ? x.z : 0.f, acc[q].z); acc[q].w = fmaf(a, live ? x.w : 0.f, acc[q].w);
                         }
                 }
 #pragma unroll
