@@ -6,20 +6,18 @@
 // gemm_tf32_128_kernel.
 //
 //   persistent CTAs, one per SM, each taking tiles of 128 rows round-robin;
-//   warps 0, 6-31      producers: every warp gathers FUSED_ROWS rows at a time (the rows' column ids
-//                      and values sit in the lanes' registers and are broadcast by shuffle; a lane
-//                      owns 4 of the 128 columns), 8 loads of 16 bytes in flight per lane;
+//   warps 0, 6-31      producers: a warp owns every 27th row of the tile; it first loads the row
+//                      pointers, column ids and values of all its rows (a lane holds one nonzero
+//                      of each row; they are broadcast by shuffle), then gathers FUSED_ROWS rows at
+//                      a time, a lane owning 4 of the 128 columns, 8 loads of 16 bytes per lane;
 //   warp 1 (one lane)  MMA issuer;   warps 2-5  epilogue.
 //   The operand ring holds two tiles of four K-blocks; a tile's four stage barriers are arrived on
 //   by every producer warp once its rows of the tile are written and fenced for the async proxy.
 // Every wait is bounded, as in the GEMM.
 //
-// Measured on B200 (two-layer forward, N = 5e6): correct, and slower than SpMM + GEMM -- 26.0 ms per
-// forward against 14.3 ms.  One thread block per SM (192 KiB of operand tiles and W) leaves the gather
-// 27 warps of 8 loads each where the stand-alone SpMM has 40 warps, every one of them with its own
-// chain of dependent rounds (row pointers, column ids, gathers), and the dense transform it saves is
-// 6 % of the forward.  It is therefore off by default (AGCN_GCN_FUSED=1 turns it on in
-// agcn_gcn2_forward_*) and kept as the measured variant.
+// Measured on B200 (two-layer forward, N = 5e6): correct, and slower than SpMM + GEMM -- 24.9 ms per
+// forward against 14.3 ms; the dense transform it saves is 6 % of the forward.  It is therefore off
+// by default (AGCN_GCN_FUSED=1 turns it on in agcn_gcn2_forward_*) and kept as the measured variant.
 #pragma once
 #include "gemm_tf32_kernels.cuh"
 #include "ptx.cuh"
@@ -31,6 +29,7 @@ constexpr int FUSED_PROD_WARPS = 27;
 constexpr int FUSED_WARPS = 2 + GEMM_EPI_WARPS + FUSED_PROD_WARPS - 1;   // warp 0 is a producer too: 32 warps
 constexpr int FUSED_THREADS = 32 * FUSED_WARPS;
 constexpr int FUSED_ROWS = 2;                         // rows a producer warp gathers at a time
+constexpr int FUSED_WARP_ROWS = (GEMM_TILE_M + FUSED_PROD_WARPS - 1) / FUSED_PROD_WARPS;   // rows of a tile per producer warp
 constexpr int FUSED_MAX_DEG = 32;                     // nonzeros of a row live in one register per lane
 constexpr int FUSED_ERR_BAD_COLUMN = 4;               // status code beside the GEMM_ERR_TIMEOUT_* ones
 constexpr int FUSED_SMEM_BYTES = 1024 /* alignment slack */ + GEMM_W_BYTES + FUSED_STAGES * GEMM_STAGE_BYTES +
@@ -168,20 +167,31 @@ gcn_fused_layer_kernel(const int *__restrict__ indptr, const int *__restrict__ i
                 break;
             }
             uint8_t *tile_base = s_ring + buf * GEMM_KBLKS * GEMM_STAGE_BYTES;
-            for (int m0 = p * FUSED_ROWS; m0 < GEMM_TILE_M; m0 += FUSED_PROD_WARPS * FUSED_ROWS) {
-                int cnt[FUSED_ROWS], pc[FUSED_ROWS];
-                float pv[FUSED_ROWS];
+            // this warp's rows of the tile: p, p + 27, ...  First every row pointer, then every row's column
+            // ids and values (a lane holds one nonzero of each row), so that the dependent loads of all
+            // rows travel together; then the gathers, FUSED_ROWS rows at a time.
+            int cnt[FUSED_WARP_ROWS], pc[FUSED_WARP_ROWS], first[FUSED_WARP_ROWS];
+            float pv[FUSED_WARP_ROWS];
+#pragma unroll
+            for (int k = 0; k < FUSED_WARP_ROWS; k++) {
+                const int m = p + k * FUSED_PROD_WARPS;
+                const int64_t r = (int64_t)tile * GEMM_TILE_M + m;
+                int a = 0, b = 0;
+                if (m < GEMM_TILE_M && r < m_rows) { a = indptr[r]; b = indptr[r + 1]; }
+                first[k] = a;
+                cnt[k] = b - a < FUSED_MAX_DEG ? b - a : FUSED_MAX_DEG;      // the host launches rows of <= 32 nonzeros only
+            }
+#pragma unroll
+            for (int k = 0; k < FUSED_WARP_ROWS; k++) {
+                pc[k] = lane < cnt[k] ? idx[first[k] + lane] : 0;
+                pv[k] = lane < cnt[k] ? val[first[k] + lane] : 0.f;
+            }
+#pragma unroll
+            for (int k0 = 0; k0 < FUSED_WARP_ROWS; k0 += FUSED_ROWS) {
                 int max_cnt = 0;
 #pragma unroll
-                for (int q = 0; q < FUSED_ROWS; q++) {
-                    const int64_t r = (int64_t)tile * GEMM_TILE_M + m0 + q;
-                    int a = 0, b = 0;
-                    if (m0 + q < GEMM_TILE_M && r < m_rows) { a = indptr[r]; b = indptr[r + 1]; }
-                    cnt[q] = b - a < FUSED_MAX_DEG ? b - a : FUSED_MAX_DEG;      // the host launches rows of <= 32 nonzeros only
-                    pc[q] = lane < cnt[q] ? idx[a + lane] : 0;
-                    pv[q] = lane < cnt[q] ? val[a + lane] : 0.f;
-                    max_cnt = max_cnt > cnt[q] ? max_cnt : cnt[q];
-                }
+                for (int q = 0; q < FUSED_ROWS; q++)
+                    if (k0 + q < FUSED_WARP_ROWS) max_cnt = max_cnt > cnt[k0 + q] ? max_cnt : cnt[k0 + q];
                 float4 acc[FUSED_ROWS];
 #pragma unroll
                 for (int q = 0; q < FUSED_ROWS; q++) acc[q] = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -192,7 +202,8 @@ gcn_fused_layer_kernel(const int *__restrict__ indptr, const int *__restrict__ i
                     for (int q = 0; q < FUSED_ROWS; q++)
 #pragma unroll
                         for (int u = 0; u < 4; u++) {
-                            int col = __shfl_sync(0xffffffffu, pc[q], (i + u) & 31);       // 0 from the lanes past the row's end
+                            if (k0 + q >= FUSED_WARP_ROWS) continue;                             // compile-time
+                            int col = __shfl_sync(0xffffffffu, pc[k0 + q], (i + u) & 31);       // 0 from the lanes past the row's end
                             const bool outside = (uint64_t)(int64_t)col >= (uint64_t)n_cols;
                             bad_column = bad_column || outside;
                             col = outside ? 0 : col;
@@ -202,8 +213,9 @@ gcn_fused_layer_kernel(const int *__restrict__ indptr, const int *__restrict__ i
                     for (int q = 0; q < FUSED_ROWS; q++)
 #pragma unroll
                         for (int u = 0; u < 4; u++) {
-                            const bool live = i + u < cnt[q];
-                            const float a = __shfl_sync(0xffffffffu, pv[q], (i + u) & 31);       // 0 past the row's end
+                            if (k0 + q >= FUSED_WARP_ROWS) continue;
+                            const bool live = i + u < cnt[k0 + q];
+                            const float a = __shfl_sync(0xffffffffu, pv[k0 + q], (i + u) & 31);       // 0 past the row's end
                             const float4 x = v[q][u];
                             acc[q].x = fmaf(a, live ? x.x : 0.f, acc[q].x); acc[q].y = fmaf(a, live ? x.y : 0.f, acc[q].y);
                             acc[q].z = fmaf(a, live ? x.z : 0.f, acc[q].z); acc[q].w = fmaf(a, live ? x.w : 0.f, acc[q].w);
@@ -211,8 +223,8 @@ gcn_fused_layer_kernel(const int *__restrict__ indptr, const int *__restrict__ i
                 }
 #pragma unroll
                 for (int q = 0; q < FUSED_ROWS; q++) {
-                    const int m = m0 + q;
-                    if (m < GEMM_TILE_M) {
+                    const int m = p + (k0 + q) * FUSED_PROD_WARPS;
+                    if (k0 + q < FUSED_WARP_ROWS && m < GEMM_TILE_M) {
                         const float4 h = make_float4(fmaxf(acc[q].x, 0.f), fmaxf(acc[q].y, 0.f), fmaxf(acc[q].z, 0.f), fmaxf(acc[q].w, 0.f));
                         // columns 4*lane .. 4*lane+3: K-block lane / 8, 16-byte chunk lane % 8, swizzled by the row
                         uint8_t *dst = tile_base + (lane >> 3) * GEMM_STAGE_BYTES + m * 128 + (((lane & 7) ^ (m & 7)) << 4);
