@@ -96,7 +96,7 @@ static int ctx_sync(agcn_host_ctx *c)
 
 // Cuts the tuple list into about `want_parts` unit ranges of equal nonzero count, reading the
 // caller's host copy of .block4 (tuples tile [0, nnz) in order, so loc_begin is monotone).
-static void plan_parts(agcn_host_ctx *c, const int *h_block4, int want_parts)
+static void plan_part_cuts(agcn_host_ctx *c, const int *h_block4, int want_parts)
 {
     const int64_t n_units = ceil_div(c->n_blocks, HOST_SPMM_WARPS);
     c->part_unit.assign(1, 0);
@@ -112,13 +112,23 @@ static void plan_parts(agcn_host_ctx *c, const int *h_block4, int want_parts)
             if ((int64_t)h_block4[4 * mid * HOST_SPMM_WARPS + 2] < target) lo = mid + 1; else hi = mid;
         }
         if (lo <= c->part_unit.back() || lo >= n_units) continue;
+        // the tuples have not been validated yet when this runs ahead of the plan: a cut is only
+        // taken where it keeps rows and nonzero offsets inside the arrays and in order
+        const int64_t row = h_block4[4 * lo * HOST_SPMM_WARPS + 1], loc = h_block4[4 * lo * HOST_SPMM_WARPS + 2];
+        if (loc <= c->part_loc.back() || loc >= c->nnz || row < c->part_row.back() || row > c->n_rows) continue;
         c->part_unit.push_back(lo);
-        c->part_row.push_back(h_block4[4 * lo * HOST_SPMM_WARPS + 1]);
-        c->part_loc.push_back(h_block4[4 * lo * HOST_SPMM_WARPS + 2]);
+        c->part_row.push_back(row);
+        c->part_loc.push_back(loc);
     }
     c->part_unit.push_back(n_units);
     c->part_row.push_back(c->n_rows);
     c->part_loc.push_back(c->nnz);
+}
+
+// The carry slots of every unit range (needs the plan's bookkeeping: build_plan).
+static void plan_part_slots(agcn_host_ctx *c)
+{
+    const int64_t n_units = ceil_div(c->n_blocks, HOST_SPMM_WARPS);
     // Carry slots are handed out in unit order (a slot for the row entering a unit from the left,
     // one for the row leaving it to the right).  The rows a unit range completes own the slots up
     // to the first slot of the row that runs on into the next range, or -- if none does -- up to the
@@ -142,6 +152,12 @@ static void plan_parts(agcn_host_ctx *c, const int *h_block4, int want_parts)
         if (uc.x >= 0 && uc.x >= next_slot) next_slot = uc.x + 1;
         if (uc.y >= 0 && uc.y >= next_slot) next_slot = uc.y + 1;
     }
+}
+
+static void plan_parts(agcn_host_ctx *c, const int *h_block4, int want_parts)
+{
+    plan_part_cuts(c, h_block4, want_parts);
+    plan_part_slots(c);
 }
 
 static int check_graph_args(agcn_host_ctx *ctx, const int *h_block4, int64_t n_blocks, const int *h_indices,
@@ -329,25 +345,36 @@ static int host_graph_and_products(agcn_host_ctx *c, const int *h_block4, int64_
     if (rc != AGCN_OK) { ctx_sync(c); return rc; }
     for (int i = 0; i < n; i++)
         AGCN_CUDA(cudaMemcpyAsync(c->xbuf[i], h_x[i], (size_t)n_cols * dims[i] * 4, cudaMemcpyHostToDevice, c->s_up));
-    rc = build_plan(c);
-    if (rc == AGCN_OK) rc = reserve_products(c, n, dims, true);       // now that the number of carry slots is known
-    if (rc != AGCN_OK) { ctx_sync(c); return rc; }
-    const auto host_t1 = std::chrono::steady_clock::now();
-    // ranges of about 32 MB of (column id, value) pairs: long enough for full PCIe speed, short
-    // enough that the first product starts early and the last download is short
-    plan_parts(c, h_block4, (int)std::max<int64_t>(1, std::min<int64_t>(64, (nnz * 8) >> 25)));
+    // Column ids and values in ranges of about 32 MB: long enough for full PCIe speed, short enough
+    // that the first product starts early and the last download is short.  Where to cut depends on the
+    // caller's .block4 alone, so EVERY upload of the call is enqueued here, before the plan is built:
+    // the copy engine then runs without a gap however long the host takes over the plan and the
+    // launches below (a busy host used to leave it idle between ranges).
+    plan_part_cuts(c, h_block4, (int)std::max<int64_t>(1, std::min<int64_t>(64, (nnz * 8) >> 25)));
     const int n_parts = (int)c->part_unit.size() - 1;
     int *idx = static_cast<int *>(c->graph[1]);
     float *val = static_cast<float *>(c->graph[2]);
+    std::vector<cudaEvent_t> part_up((size_t)n_parts);
     for (int k = 0; k < n_parts; k++) {
         const int64_t p0 = c->part_loc[k], p1 = c->part_loc[k + 1];
         AGCN_CUDA(cudaMemcpyAsync(idx + p0, h_indices + p0, (size_t)(p1 - p0) * 4, cudaMemcpyHostToDevice, c->s_up));
         AGCN_CUDA(cudaMemcpyAsync(val + p0, h_vals + p0, (size_t)(p1 - p0) * 4, cudaMemcpyHostToDevice, c->s_up));
-        if (k == n_parts - 1) AGCN_CUDA(cudaEventRecord(c->t_up1, c->s_up));
-        rc = ctx_chain(c, c->s_up, c->s_run);
+        rc = ctx_event(c, &part_up[k]);
+        if (rc != AGCN_OK) { ctx_sync(c); return rc; }
+        AGCN_CUDA(cudaEventRecord(part_up[k], c->s_up));
+    }
+    AGCN_CUDA(cudaEventRecord(c->t_up1, c->s_up));
+    rc = build_plan(c);               // on the host and on s_run, under the uploads
+    if (rc == AGCN_OK) rc = reserve_products(c, n, dims, true);       // now that the number of carry slots is known
+    if (rc != AGCN_OK) { ctx_sync(c); return rc; }
+    plan_part_slots(c);
+    const auto host_t1 = std::chrono::steady_clock::now();
+    for (int k = 0; k < n_parts; k++) {
+        const int64_t p0 = c->part_loc[k], p1 = c->part_loc[k + 1];
+        AGCN_CUDA(cudaStreamWaitEvent(c->s_run, part_up[k], 0));
         if (k == 0) AGCN_CUDA(cudaEventRecord(c->t_run0, c->s_run));
         // a column id outside [0, n_cols) sets the abort word, and every kernel behind it returns at once
-        if (rc == AGCN_OK) rc = spmm_check_cols(idx + p0, p1 - p0, n_cols, c->d_abort, c->s_run);
+        rc = spmm_check_cols(idx + p0, p1 - p0, n_cols, c->d_abort, c->s_run);
         for (int i = 0; i < n && rc == AGCN_OK; i++) {
             SpmmLaunchPart part;
             part.unit0 = c->part_unit[k]; part.unit1 = c->part_unit[k + 1];

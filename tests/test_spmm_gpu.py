@@ -587,6 +587,35 @@ def test_host_batch_and_streamed_graph(cfg1, cfg4_small):
         h.close()
 
 
+def test_streamed_graph_in_several_ranges_and_malformed_block4():
+    # a graph large enough (2.4e7 nonzeros) for the streamed call to cut A into several upload ranges:
+    # bit-identical to the resident product; and tuples that would put a cut outside the arrays or out of
+    # order (the cuts are taken from the caller's .block4 before the plan has validated it) are an error,
+    # not a fault
+    from accelgcn import spmm
+    c = Case(2, 0.2)
+    assert len(c.idx) * 8 >> 25 >= 4
+    h = spmm.HostSpmm()
+    xs = [np.ascontiguousarray(c.x(d)) for d in (32, 64)]
+    ys = h.step_batch(c.block4, c.idx, c.val, xs, c.n)
+    for x, y in zip(xs, ys):
+        assert np.array_equal(y, c.run(x))
+    n_units = (len(c.block4) + 7) // 8
+    for unit, loc in ((n_units // 3, len(c.idx) + 5), (n_units // 2, 3), (2 * n_units // 3, -7)):
+        bad = c.block4.copy()
+        bad[unit * 8, 2] = loc
+        with pytest.raises(spmm._lib.AccelGcnError):
+            h.step_batch(bad, c.idx, c.val, xs, c.n)
+    bad = c.block4.copy()
+    bad[(n_units // 2) * 8, 1] = c.n + 1                 # row of a unit's first tuple past the matrix
+    with pytest.raises(spmm._lib.AccelGcnError):
+        h.step_batch(bad, c.idx, c.val, xs, c.n)
+    ys_again = h.step_batch(c.block4, c.idx, c.val, xs, c.n)           # the context is still good
+    for a, b in zip(ys_again, ys):
+        assert np.array_equal(a, b)
+    h.close()
+
+
 def test_cpp_harness_full_sweep_mode(cfg1, tmp_path):
     # spmm_test with no arguments: every graph of ../graphs at every dim 16..128 step 1
     # (main.cu:195-219), here on two small graphs; with checking forced on, every product validates
