@@ -445,9 +445,11 @@ plan_check_kernel(const int4 *__restrict__ block4, int64_t n_blocks, int64_t n_r
     if (e > n_blocks) return;
     int err = 0;
     int64_t prev_end = 0;       // first row not covered by tuples before e
+    int64_t prev_loc_end = 0;   // first nonzero not covered by tuples before e
     if (e > 0) {
         const int4 a = block4[e - 1];
         prev_end = (int64_t)a.y + tuple_rows(a);
+        prev_loc_end = (int64_t)a.z + (tuple_is_big(a) ? (int64_t)a.w : (int64_t)tuple_rows(a) * a.x);
     }
     if (e == n_blocks) {
         gap[e] = prev_end <= n_rows ? (int)(n_rows - prev_end) : 0;
@@ -458,7 +460,9 @@ plan_check_kernel(const int4 *__restrict__ block4, int64_t n_blocks, int64_t n_r
     const int rows = tuple_rows(b);
     const int64_t nz = big ? (int64_t)b.w : (int64_t)rows * b.x;
     if (b.x < 1 || rows < 1 || nz < 1 || nz > SPMM_DEG_BOUND) err |= SPMM_ERR_TUPLE;
-    if (b.z < 0 || (int64_t)b.z + nz > nnz) err |= SPMM_ERR_LOC;
+    // tuples take their nonzeros in order and without overlap (what lets A be uploaded and multiplied
+    // range by range: a tuple never reaches into a range that has not arrived)
+    if (b.z < 0 || (int64_t)b.z + nz > nnz || (int64_t)b.z < prev_loc_end) err |= SPMM_ERR_LOC;
     int64_t g = (int64_t)b.y - prev_end;
     if (big && e > 0) {
         // a later chunk of the same heavy row repeats its row id

@@ -72,7 +72,7 @@ int spmm_create(agcn_spmm_plan **out, const int *d_block4, int64_t n_blocks, con
         set_error("agcn_spmm_create: invalid input:%s%s%s%s",
                   (err & SPMM_ERR_TUPLE) ? " malformed .block4 tuple;" : "",
                   (err & SPMM_ERR_ROW) ? " tuple rows out of range or not ascending;" : "",
-                  (err & SPMM_ERR_LOC) ? " tuple nonzero range outside [0, nnz);" : "",
+                  (err & SPMM_ERR_LOC) ? " tuple nonzero range outside [0, nnz) or out of order;" : "",
                   (err & SPMM_ERR_COL) ? " column index outside [0, n_cols);" : "");
         return AGCN_ERR_RANGE;
     }
