@@ -345,12 +345,16 @@ static int host_graph_and_products(agcn_host_ctx *c, const int *h_block4, int64_
     if (rc != AGCN_OK) { ctx_sync(c); return rc; }
     for (int i = 0; i < n; i++)
         AGCN_CUDA(cudaMemcpyAsync(c->xbuf[i], h_x[i], (size_t)n_cols * dims[i] * 4, cudaMemcpyHostToDevice, c->s_up));
+    rc = build_plan(c);               // on the host and on s_run, under the uploads of X
+    if (rc == AGCN_OK) rc = reserve_products(c, n, dims, true);       // now that the number of carry slots is known
+    if (rc != AGCN_OK) { ctx_sync(c); return rc; }
+    const auto host_t1 = std::chrono::steady_clock::now();
     // Column ids and values in ranges of about 32 MB: long enough for full PCIe speed, short enough
-    // that the first product starts early and the last download is short.  Where to cut depends on the
-    // caller's .block4 alone, so EVERY upload of the call is enqueued here, before the plan is built:
-    // the copy engine then runs without a gap however long the host takes over the plan and the
-    // launches below (a busy host used to leave it idle between ranges).
-    plan_part_cuts(c, h_block4, (int)std::max<int64_t>(1, std::min<int64_t>(64, (nnz * 8) >> 25)));
+    // that the first product starts early and the last download is short.  Every upload is enqueued
+    // before the first launch, so that the copy engine runs without a gap however long the host
+    // takes over the launches below.  (Enqueued ahead of the plan build they delay it: its small
+    // device-to-host copies then wait behind them.)
+    plan_parts(c, h_block4, (int)std::max<int64_t>(1, std::min<int64_t>(64, (nnz * 8) >> 25)));
     const int n_parts = (int)c->part_unit.size() - 1;
     int *idx = static_cast<int *>(c->graph[1]);
     float *val = static_cast<float *>(c->graph[2]);
@@ -364,11 +368,6 @@ static int host_graph_and_products(agcn_host_ctx *c, const int *h_block4, int64_
         AGCN_CUDA(cudaEventRecord(part_up[k], c->s_up));
     }
     AGCN_CUDA(cudaEventRecord(c->t_up1, c->s_up));
-    rc = build_plan(c);               // on the host and on s_run, under the uploads
-    if (rc == AGCN_OK) rc = reserve_products(c, n, dims, true);       // now that the number of carry slots is known
-    if (rc != AGCN_OK) { ctx_sync(c); return rc; }
-    plan_part_slots(c);
-    const auto host_t1 = std::chrono::steady_clock::now();
     for (int k = 0; k < n_parts; k++) {
         const int64_t p0 = c->part_loc[k], p1 = c->part_loc[k + 1];
         AGCN_CUDA(cudaStreamWaitEvent(c->s_run, part_up[k], 0));
