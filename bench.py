@@ -386,14 +386,15 @@ def ours(args, rank, world, local_rank):
     # (--slices S: widths of at least --slices-min-dim columns exchange their operand in S row slices and
     # multiply slice by slice, on a second context of the same layout; narrower widths keep one slice)
     sliced = world > 1 and args.slices > 1
-    # rows x features (--feature-groups F): a width of at least F * --feature-groups-min-width columns is
+    # rows x features (--feature-groups F): a product of at least --feature-groups-min-dim columns is
     # multiplied as F independent row-sharded products of dim / F columns, each over world / F ranks with its
     # own communicator -- 1 / F of the exchange among 1 / F of the ranks, blocks of F times the rows
     fg = 1
     if world > 1:
-        fg = args.feature_groups if args.feature_groups > 0 else (2 if world % 2 == 0 else 1)
+        fg = args.feature_groups if args.feature_groups > 0 else (4 if world % 8 == 0 else 2 if world % 2 == 0 else 1)
         assert world % fg == 0, "--feature-groups must divide the number of GPUs"
-    fg_dims = [d for d in dims if fg > 1 and not sliced and d % fg == 0 and d // fg >= args.feature_groups_min_width]
+    fg_dims = [d for d in dims if fg > 1 and not sliced and d % fg == 0 and d >= args.feature_groups_min_dim
+               and d // fg >= args.feature_groups_min_width]
     shard = sharded.ShardedSpmm(ip, ix, v, rank, world)
     shard_of = {d: shard for d in dims}
     col_of = {d: (0, d) for d in dims}
@@ -1118,8 +1119,9 @@ def main():
     ap.add_argument("--no-ref-gpu", action="store_true", help="skip timing the reference's GPU kernels")
     ap.add_argument("--feature-groups", type=int, default=0,
                     help="several GPUs: multiply wide operands as this many independent products of dim / F columns, each "
-                         "row-sharded over world / F ranks (0 = 2 on an even number of GPUs, else 1)")
-    ap.add_argument("--feature-groups-min-width", type=int, default=64, help="narrowest dim / F that --feature-groups applies to")
+                         "row-sharded over world / F ranks (0 = 4 on eight GPUs, 2 on two or four, else 1)")
+    ap.add_argument("--feature-groups-min-dim", type=int, default=128, help="narrowest product that --feature-groups applies to")
+    ap.add_argument("--feature-groups-min-width", type=int, default=32, help="narrowest dim / F that --feature-groups applies to")
     ap.add_argument("--no-gcn", action="store_true", help="default workload: leave out the short configuration-5 forward (`gcn` record)")
     ap.add_argument("--dim", type=int, default=64, help="dense width of the replicas workload")
     ap.add_argument("--kernel-only", action="store_true", help="resident-data loop only (for profiling under ncu)")
