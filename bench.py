@@ -665,6 +665,9 @@ def ours(args, rank, world, local_rank):
         per_dim.append(row)
     top = max(per_dim, key=lambda r: r["ms"])
     variant = "column-tiled" if top["dim"] in tiled else ("two 64-column passes" if top["dim"] > 64 else "one pass")
+    if world > 1:
+        variant = (f"{fg} feature groups of {world // fg} row blocks" if top["dim"] in fg_dims
+                   else "row blocks, column ranges" if ranges_of[top["dim"]] != 1 else "row blocks")
     traffic = NCU_TRAFFIC_BYTES.get((args.workload, top["dim"], variant)) if world == 1 else None
     # `bound`/`achieved`/`frac` follow the contract: compulsory HBM bytes per launch over the CUDA-event
     # time against the measured copy bandwidth.  Which resource really binds is named beside it.
